@@ -25,9 +25,10 @@ extern "C" {
 #endif
 
 enum { GTB_SEQ_BF16 = 0, GTB_SEQ_F32 = 1 };                       /* compute mode */
-enum { GTB_MIX_SIGMOID_ATTN = 1, GTB_MIX_RETENTION = 2, GTB_MIX_MINGRU = 3, GTB_MIX_SOFTMAX_ATTN = 4 };   /* branch kinds of a token mixer */
-enum { GTB_BLOCK_PARALLEL = 0, GTB_BLOCK_POSTNORM = 1 };          /* layer styles */
-enum { GTB_FF_GEGLU = 0, GTB_FF_POLYNORM = 1, GTB_FF_EXPERTS = 2 };   /* feed-forward kinds */
+enum { GTB_MIX_SIGMOID_ATTN = 1, GTB_MIX_RETENTION = 2, GTB_MIX_MINGRU = 3, GTB_MIX_SOFTMAX_ATTN = 4, GTB_MIX_LATENT_ATTN = 5 };   /* branch kinds of a token mixer */
+enum { GTB_BLOCK_PARALLEL = 0, GTB_BLOCK_POSTNORM = 1, GTB_BLOCK_PRENORM = 2 };          /* layer styles */
+enum { GTB_FF_GEGLU = 0, GTB_FF_POLYNORM = 1, GTB_FF_EXPERTS = 2, GTB_FF_GATED_EXPERTS = 3 };   /* feed-forward kinds */
+enum { GTB_NORM_RMS = 0, GTB_NORM_DYT = 1 };                      /* norm of a pre-norm layer and of the model's output */
 enum { GTB_ROT_HALVES = 0, GTB_ROT_INTERLEAVED = 1 };             /* which entries a rotary pair takes: (i, i + dims/2) or (2i, 2i + 1) */
 
 /* One branch of a token mixer.  Tensors of branch b of layer i are "l<i>.mix.<name>.{q,k,v,o,...}".
@@ -47,7 +48,15 @@ enum { GTB_ROT_HALVES = 0, GTB_ROT_INTERLEAVED = 1 };             /* which entri
  *    when pool > 0, one mean key / mean value for every block [b pool, (b + 1) pool) that ends at or before i - window; sink: the
  *    denominator also holds exp(sink[head]); gated 2: output times logistic(g h) (1: silu) before the out projection; kv_from >= 0:
  *    no k / v tensors, keys and values are those of layer kv_from's cache (an earlier GTB_MIX_SOFTMAX_ATTN layer with the same
- *    kv_heads, dim, vdim).  Tensors q, k, v, q.norm, k.norm, sink, g, o. */
+ *    kv_heads, dim, vdim).  Tensors q, k, v, q.norm, k.norm, sink, g, o.
+ *  GTB_MIX_LATENT_ATTN: softmax attention whose keys and values are up-projections of one latent per token.  Every head has `dim`
+ *    plain and `rope_dim` rotated query/key entries ([plain | rotated] per head in q) and `vdim` value entries.  dkv h has kv_rank +
+ *    rope_dim rows: the first kv_rank, scaled to unit RMS (eps of the model) times dkv.norm, are the latent c; the last rope_dim,
+ *    rotated, are one key part shared by all heads.  Plain keys uk c and values uv c per head; score = scale (q_plain . k_plain +
+ *    q_rot . k_rot).  q_rank > 0: q = uq (unit-RMS(dq h) * dq.norm) instead of q h.  Rotation on the first rot_dims (<= rope_dim)
+ *    entries of the rotated part in rot_layout.  window, sink as for GTB_MIX_SOFTMAX_ATTN (no pooled blocks); gated 3: head a's output
+ *    times logistic(g h)_a, g with one row per head.  The slot caches only c and the rotated key part ([kv_rank + rope_dim] per token).
+ *    Tensors q | dq, dq.norm, uq; dkv, dkv.norm, uk, uv, sink, g, o. */
 typedef struct {
     int kind;
     char name[16];
@@ -65,25 +74,39 @@ typedef struct {
     int window, pool;                /* 0: every earlier token / no pooled blocks */
     int sink;                        /* 1: learned per-head sink in the softmax denominator */
     int kv_from;                     /* -1: own keys and values */
+    int rope_dim, kv_rank, q_rank;   /* GTB_MIX_LATENT_ATTN */
 } gtb_seq_branch;
 
 /* Tensors of layer i beyond its branches'.  Parallel blocks: "l<i>.norm1" (one gain), "l<i>.mlp.{gate,up,down}", "l<i>.canon{1,2}".
  * Post-norm layers: "l<i>.norm1", "l<i>.norm2" [width] (norm2 only with a feed-forward); GTB_FF_POLYNORM: "l<i>.mlp.up" [ff][width],
  * "l<i>.mlp.down" [width][ff], "l<i>.mlp.act" [4]; GTB_FF_EXPERTS: "l<i>.mlp.router" [experts + identity][width], "l<i>.mlp.correction"
  * [experts + identity], "l<i>.mlp.e<j>.up" [ff][width], "l<i>.mlp.e<j>.down" [width][ff].  A branch with an empty name has its tensors
- * directly under "l<i>.mix.". */
+ * directly under "l<i>.mix.".
+ * Pre-norm layers: "l<i>.norm<q>" [width] and, for GTB_NORM_DYT, "l<i>.norm<q>.alpha" [] and "l<i>.norm<q>.b" [width]; with streams > 0
+ * "l<i>.hc<q>.in" [streams], "l<i>.hc<q>.out" [streams], "l<i>.hc<q>.mix" [streams][streams] (q = 1: mixer, 2: feed-forward);
+ * GTB_FF_GEGLU: "l<i>.mlp.{gate,up,down}"; GTB_FF_GATED_EXPERTS: "l<i>.mlp.router" [experts][width], "l<i>.mlp.e<j>.{gate,up,down}" and,
+ * when shared_ff > 0, "l<i>.mlp.shared.{gate,up,down}" with inner width shared_ff and "l<i>.mlp.shared.sg" [1][width]. */
 typedef struct {
     int n_branches;                  /* 1 or 2 */
     gtb_seq_branch branch[2];
     int ff;                          /* 0: no feed-forward; else its inner width (of one expert for GTB_FF_EXPERTS) */
     int style;                       /* GTB_BLOCK_PARALLEL: x += mixer(h) + ff(h), h = gain-norm(x) (+ convolutions);
                                       * GTB_BLOCK_POSTNORM: x += norm1(mixer(x)); x += norm2(ff(x)), norms with weight vectors (1 + w),
-                                      * one branch, out_scale unused */
+                                      * one branch, out_scale unused;
+                                      * GTB_BLOCK_PRENORM: x += mixer(norm1(x)); x += ff(norm2(x)), norm of kind norm_kind; with config.streams > 0
+                                      * the stream is kept in `streams` copies: sublayer q reads u = sum_s hc<q>.in[s] x_s and all copies are
+                                      * rewritten at once from the old ones, x_t <- sum_s hc<q>.mix[s][t] x_s + hc<q>.out[t] y.  One branch
+                                      * (GTB_MIX_LATENT_ATTN) */
     int ff_kind;                     /* GTB_FF_GEGLU: down(gelu_tanh(gate h) * (up h)); GTB_FF_POLYNORM: down(a N(z) + b N(z^2) + c N(z^3) + e),
                                       * z = up h, N = unit RMS over the ff values, (a, b, c, e) = tensor mlp.act; GTB_FF_EXPERTS: router outputs
                                       * 0 .. experts-1 are experts e<i>.down(relu(e<i>.up h)^2), the `identity` outputs after them return h;
-                                      * s = softmax(router h), the `top` largest s + correction are chosen and weighted with their s */
+                                      * s = softmax(router h), the `top` largest s + correction are chosen and weighted with their s;
+                                      * GTB_FF_GATED_EXPERTS: experts e<i>.down(silu(e<i>.gate h) * (e<i>.up h)); s = logistic(router h) in fp32, the
+                                      * `top` largest s are chosen (ties to the lower index) and weighted with s / (sum of the chosen s + 1e-20);
+                                      * shared_ff > 0: an expert of that inner width runs for every row, times logistic(shared.sg h) */
     int experts, top, identity;
+    int norm_kind;                   /* GTB_BLOCK_PRENORM: GTB_NORM_RMS (x / rms(x) * w) or GTB_NORM_DYT (tanh(alpha x) * w + b, no statistics) */
+    int shared_ff;
 } gtb_seq_layer;
 
 typedef struct {
@@ -96,7 +119,10 @@ typedef struct {
     int n_slots, max_ctx;            /* sequences held at once; positions per slot */
     int max_rows;                    /* rows per pass over the weights (longer steps are cut into passes); 0: default */
     float embed_scale;               /* embedding rows are multiplied by this (0 counts as 1) */
-    int final_norm;                  /* 0: one gain; 1: weight vector stored around zero (1 + w) */
+    int final_norm;                  /* 0: one gain; 1: weight vector stored around zero (1 + w); 2: Dynamic Tanh, tensors final.norm, final.norm.alpha, final.norm.b */
+    int streams;                     /* pre-norm layers: copies of the residual stream under hyper-connections (all equal to the embedding output at
+                                      * the start, summed at the end); 0: one stream, plain residual sum */
+    float logit_softcap;             /* > 0: logits <- cap * tanh(logits / cap) */
 } gtb_seq_config;
 
 typedef struct gtb_seq_model* gtb_seq_t;

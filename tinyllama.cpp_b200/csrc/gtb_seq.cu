@@ -11,6 +11,10 @@
 //    projection into a fresh block Y, x += norm1(Y); then the feed-forward the same way.  Experts' up matrices are stacked along N
 //    ([experts * ff][width]) and their down matrices are stored one after the other ([experts][width][ff padded to 64]), which is what
 //    both the per-row kernels and the grouped product read.
+//  * pre-norm layers (GTB_BLOCK_PRENORM) keep the stream in `streams` copies XS [streams][max_rows][width]; one kernel per sublayer
+//    boundary applies the finished sublayer's update to all copies and forms the next sublayer's normalised input.  Latent attention
+//    caches [latent | rotated key part] per token ([n_slots][max_ctx][c_ld]); gated experts store [gate | up] of every expert as one
+//    block of 2 ff rows ([experts][2 ff][width]), the shared expert's gate as one more row of the router matrix.
 #include <math.h>
 #include <string.h>
 
@@ -25,6 +29,7 @@
 #include "gtb_seq_kernels.cuh"
 #include "gtb_seq_mixers.cuh"
 #include "gtb_seq_mixers_tiled.cuh"
+#include "gtb_seq_latent.cuh"
 
 using namespace gtb;
 using namespace gtb::seq;
@@ -53,6 +58,10 @@ struct BranchW {
     float* d_decay = nullptr;
     float* d_inv_freq = nullptr;
     float *d_qnorm = nullptr, *d_knorm = nullptr, *d_sink = nullptr;
+    // latent attention
+    bf16 *w_uq = nullptr, *w_uk = nullptr, *w_uv = nullptr;
+    float* d_kvnorm = nullptr;
+    int kv_off = 0, c_ld = 0, rank_p = 0, qrank_p = 0;
 };
 
 struct LayerW {
@@ -70,7 +79,13 @@ struct LayerW {
     bf16 *w_up = nullptr, *w_down = nullptr, *w_router = nullptr;
     float *d_act = nullptr, *d_corr = nullptr;
     int kfp = 0;               // inner width of the feed-forward (of one expert), padded to 64
-    int n_out = 0;             // router outputs: experts + identity
+    int n_out = 0;             // router outputs: experts + identity (gated experts: + 1 for the shared expert's gate)
+    // pre-norm style
+    float *nb[2] = {nullptr, nullptr}, *na[2] = {nullptr, nullptr};     // Dynamic Tanh: bias vectors and alpha of norm1 / norm2
+    float* hc[2] = {nullptr, nullptr};                                  // hyper-connection weights [in | out | mix] of the two sublayers
+    bf16 *w_sh_gu = nullptr, *w_sh_down = nullptr;                      // shared expert
+    int sff = 0, sff_p = 0;
+    bool sh_inter = false, e_inter = false;                             // [gate | up] rows interleaved in groups of 32
 };
 
 struct Run {
@@ -95,7 +110,13 @@ struct gtb_seq_model {
     int wp = 0;                                  // padded width
     size_t weight_bytes = 0, state_bytes = 0;
     bf16 *embed = nullptr, *bigram = nullptr, *head = nullptr, *loop_in = nullptr;
-    float *loop_step = nullptr, *final_gain = nullptr;
+    float *loop_step = nullptr, *final_gain = nullptr, *final_b = nullptr, *final_a = nullptr;
+    // pre-norm style: copies of the stream, latent attention workspace, shared expert
+    int ns = 1;                                  // copies of the stream
+    bool prenorm = false;
+    float *xs = nullptr, *hc_one = nullptr, *latQ = nullptr, *latQA = nullptr, *Y2 = nullptr, *shw = nullptr;
+    void *opQ = nullptr, *opO = nullptr;
+    int lat_q_max = 0, lat_qa_max = 0, lat_qr_max = 0, lat_ol_max = 0;
     // workspace of a pass
     int max_rows = 0, n1_max = 0, ff_max = 0, kout_p_max = 0, ro_max = 0;
     float* Y = nullptr;                          // fresh output block of an accumulating tensor-core product [max_rows][width]
@@ -419,6 +440,143 @@ int run_postnorm_layer(gtb_seq_model* m, const PassTables& t, int R, int S, cons
     return GTB_OK;
 }
 
+// ---- pre-norm layers ---------------------------------------------------------------------------------------------------------
+// a finished sublayer whose update of the stream copies has not been applied yet
+struct PendingUpdate { const float* Y = nullptr; const float* Y2 = nullptr; const float* hc = nullptr; int src_ns = 1; };
+
+NormArgs norm_args(const gtb_seq_model* m, const LayerW& l, int q) {
+    NormArgs n{};
+    n.kind = l.d.norm_kind; n.w = q == 0 ? l.norm1 : l.norm2; n.b = l.nb[q]; n.alpha = l.na[q]; n.eps = m->cfg.eps;
+    return n;
+}
+// applies the pending update (if any) to the copies and forms the next sublayer's input in opA (hc_next: its [in | out | mix]; null: none)
+template <typename OT>
+int hc_boundary(gtb_seq_model* m, int R, PendingUpdate& pend, const float* hc_next, const NormArgs& nrm, float* xsum) {
+    const int W = m->cfg.width;
+    k_hc_step<OT><<<R, 256, 0, ctx().stream>>>(m->xs, (size_t)m->max_rows * W, m->ns, pend.src_ns, W, pend.Y, pend.Y2, pend.hc, hc_next, nrm, (OT*)m->opA, m->wp, xsum);
+    GTB_LAUNCHED();
+    pend = PendingUpdate{};
+    pend.src_ns = m->ns;
+    return GTB_OK;
+}
+
+LatAttn lat_args(const gtb_seq_model* m, const BranchW& b) {
+    LatAttn a{};
+    a.heads = b.d.heads; a.dim = b.d.dim; a.rope = b.d.rope_dim; a.vdim = b.d.vdim; a.rank = b.d.kv_rank; a.q_rank = b.d.q_rank;
+    a.rot_dims = b.d.rot_dims; a.rot_layout = b.d.rot_layout; a.inv_freq = b.d_inv_freq; a.kv_norm = b.d_kvnorm; a.q_norm = b.d_qnorm;
+    a.eps = m->cfg.eps; a.q_off = b.q_off; a.kv_off = b.kv_off; a.g_off = b.g_off; a.a_off = b.a_off; a.c_ld = b.c_ld; a.max_ctx = m->cfg.max_ctx;
+    return a;
+}
+// the absorbed form as a softmax attention with one K/V head over the latent cache: keys [latent | rotated part], values the latent
+SoftAttn lat_soft_args(const gtb_seq_model* m, const BranchW& b) {
+    SoftAttn a{};
+    a.heads = b.d.heads; a.kv_heads = 1; a.dim = b.d.kv_rank + b.d.rope_dim; a.vdim = b.d.kv_rank;
+    a.scale = b.d.scale; a.eps = m->cfg.eps; a.window = b.d.window; a.sink = b.d_sink;
+    a.k_ld = a.v_ld = b.c_ld; a.own_kv = 1; a.max_ctx = m->cfg.max_ctx;
+    return a;
+}
+
+// One pre-norm layer on R rows.  pend carries the update of the sublayer before it (none for the first layer) and leaves with this
+// layer's last sublayer pending; cap_prev: where the sum of the copies after the previous layer goes (capture), or null.
+template <typename OT>
+int run_prenorm_layer(gtb_seq_model* m, const PassTables& t, int R, int S, const Run& run, const LayerW& l, bool portions, PendingUpdate& pend, float* cap_prev) {
+    cudaStream_t st = ctx().stream;
+    const gtb_seq_config& c = m->cfg;
+    const int W = c.width, wp = m->wp;
+    OT *opA = (OT*)m->opA, *opC = (OT*)m->opC;
+    int rc = hc_boundary<OT>(m, R, pend, l.hc[0], norm_args(m, l, 0), cap_prev);
+    if (rc) return rc;
+    rc = product<OT>(m, opA, wp, l.w_mix, wp, m->P, l.n1, R, l.n1, wp, nullptr, 0);
+    if (rc) return rc;
+    const BranchW& b = l.br[0];
+    {
+        const LatAttn a = lat_args(m, b);
+        const int hd = a.dim + a.rope;
+        k_lat_prep<OT><<<R, 128, 0, st>>>(t, a, m->P, l.n1, (OT*)run.kc[0], (OT*)m->opQ, b.qrank_p);
+        GTB_LAUNCHED();
+        const float* Q = m->P;
+        int ldq = l.n1, q0 = b.q_off;
+        if (a.q_rank > 0) {
+            rc = product<OT>(m, m->opQ, b.qrank_p, b.w_uq, b.qrank_p, m->latQ, a.heads * hd, R, a.heads * hd, b.qrank_p, nullptr, 0);
+            if (rc) return rc;
+            Q = m->latQ; ldq = a.heads * hd; q0 = 0;
+        }
+        k_lat_qabs<<<dim3(R, a.heads), 128, hd * sizeof(float), st>>>(t, a, Q, ldq, q0, b.w_uk, b.rank_p, m->latQA);
+        GTB_LAUNCHED();
+        const SoftAttn sa = lat_soft_args(m, b);
+        const int ldqa = a.heads * sa.dim, ld_ol = (a.heads * a.rank + 7) / 8 * 8;
+        const size_t smem = (sa.dim + 128 + 33) * sizeof(float);
+        bool done = false;
+        if (!portions && R <= SPLIT_MAX_ROWS && m->sattn_part) {
+            const int max_keys = sa.window > 0 ? std::min(c.max_ctx, sa.window) : c.max_ctx;
+            const int splits = std::max(1, std::min(32, (max_keys + 127) / 128));
+            if (splits > 1) {
+                k_sattn_split<OT><<<dim3(R, sa.heads, splits), 128, smem, st>>>(t, sa, m->latQA, ldqa, (const OT*)run.kc[0], (const OT*)run.kc[0], nullptr, nullptr, m->sattn_part, R);
+                GTB_LAUNCHED();
+                k_sattn_join<OT><<<dim3(R, sa.heads), 128, 0, st>>>(sa, m->latQA, ldqa, m->sattn_part, R, splits, (OT*)m->opO, ld_ol);
+                GTB_LAUNCHED();
+                done = true;
+            }
+        }
+        if (!done) {
+            k_sattn<OT><<<dim3(R, sa.heads), 128, smem, st>>>(t, sa, m->latQA, ldqa, (const OT*)run.kc[0], (const OT*)run.kc[0], nullptr, nullptr, (OT*)m->opO, ld_ol);
+            GTB_LAUNCHED();
+        }
+        const int n_out = a.heads * a.vdim;
+        k_lat_vup<OT><<<dim3(R, std::max(1, std::min(std::max(1, 4096 / R), (n_out + 7) / 8))), 256, 0, st>>>(a, (const OT*)m->opO, ld_ol, b.w_uv, b.rank_p, m->P, l.n1, b.d.gated, opC, l.kout_p);
+        GTB_LAUNCHED();
+    }
+    rc = product<OT>(m, opC, l.kout_p, l.w_out, l.kout_p, m->Y, W, R, W, l.kout_p, nullptr, 0);
+    if (rc) return rc;
+    pend.Y = m->Y; pend.hc = l.hc[0];
+    if (l.ff == 0) return GTB_OK;
+    rc = hc_boundary<OT>(m, R, pend, l.hc[1], norm_args(m, l, 1), nullptr);
+    if (rc) return rc;
+    if (l.d.ff_kind == GTB_FF_GEGLU) {
+        bool act_done = false;
+        if (sizeof(OT) == 2 && m->use_tensor && m->gp && R >= m->tensor_min_rows && l.gu_inter) {
+            rc = seq_gemm_bf16_geglu(m->gp, opA, wp, l.w_gu, wp, opC, l.kfp, 0, R, 2 * l.ff, wp);
+            if (rc > 0) return rc;
+            if (rc == 0) { ctx().launches++; act_done = true; }
+        }
+        if (!act_done) {
+            rc = product<OT>(m, opA, wp, l.w_gu, wp, m->G, 2 * l.ff, R, 2 * l.ff, wp, nullptr, 0);
+            if (rc) return rc;
+            const size_t n = (size_t)R * l.ff;
+            k_geglu<OT><<<(unsigned)((n + 255) / 256), 256, 0, st>>>(m->G, l.ff, opC, l.kfp, 0, R, l.gu_inter ? 1 : 0);
+            GTB_LAUNCHED();
+        }
+        rc = product<OT>(m, opC, l.kfp, l.w_down, l.kfp, m->Y, W, R, W, l.kfp, nullptr, 0);
+        if (rc) return rc;
+        pend.Y = m->Y; pend.hc = l.hc[1];
+        return GTB_OK;
+    }
+    // gated routed experts: router (and the shared expert's gate) in one product, fp32 accumulation
+    const int E = l.d.experts, top = l.d.top;
+    rc = product<OT>(m, opA, wp, l.w_router, wp, m->rl, l.n_out, R, l.n_out, wp, nullptr, 0);
+    if (rc) return rc;
+    k_moe_route_sigmoid<<<R, 32, E * sizeof(float), st>>>(m->rl, l.n_out, E, top, m->sel_idx, m->sel_w, l.sff > 0 ? m->shw : nullptr);
+    GTB_LAUNCHED();
+    if (l.sff > 0) {
+        rc = product<OT>(m, opA, wp, l.w_sh_gu, wp, m->G, 2 * l.sff, R, 2 * l.sff, wp, nullptr, 0);
+        if (rc) return rc;
+        k_swiglu_rows<OT><<<R, 256, 0, st>>>(m->G, l.sff, l.sh_inter ? 1 : 0, m->shw, opC, l.sff_p);
+        GTB_LAUNCHED();
+        rc = product<OT>(m, opC, l.sff_p, l.w_sh_down, l.sff_p, m->Y2, W, R, W, l.sff_p, nullptr, 0);
+        if (rc) return rc;
+        pend.Y2 = m->Y2;
+    }
+    {
+        const int cta_budget = std::max(1, 4096 / std::max(1, R * top));
+        k_moe_gu_rows<OT><<<dim3(R * top, std::max(1, std::min(cta_budget, (l.kfp + 7) / 8))), 256, 0, st>>>(opA, wp, wp, l.w_up, wp, l.ff, l.kfp, l.e_inter ? 1 : 0, top, m->sel_idx, m->sel_w, (OT*)m->act);
+        GTB_LAUNCHED();
+        k_moe_down_rows<OT><<<dim3(R, std::max(1, std::min(std::max(1, 4096 / R), (W + 7) / 8))), 256, 0, st>>>((const OT*)m->act, l.kfp, l.w_down, W, E, top, m->sel_idx, m->Y, W);
+        GTB_LAUNCHED();
+    }
+    pend.Y = m->Y; pend.hc = l.hc[1];
+    return GTB_OK;
+}
+
 // the launch sequence of one pass: R rows of S segments whose tables are already on the device
 template <typename OT>
 int run_pass(gtb_seq_model* m, const PassTables& t, int R, int S, bool from_pending, int n_want, const int* d_want, const int* seg_lens = nullptr) {
@@ -434,12 +592,27 @@ int run_pass(gtb_seq_model* m, const PassTables& t, int R, int S, bool from_pend
     GTB_LAUNCHED();
     const bool first_reads_x = m->L[m->runs[0].layer].d.style == GTB_BLOCK_POSTNORM;
     k_embed<OT><<<R, 256, 0, st>>>(t, m->embed, m->bigram, c.bigram_buckets, c.bigram_mul_prev, c.bigram_mul_cur, W, c.embed_scale != 0.0f ? c.embed_scale : 1.0f,
-                                   m->x, c.loop_times > 0 ? m->x0 : nullptr, first_reads_x ? opA : (OT*)nullptr, wp);
+                                   m->prenorm ? m->xs : m->x, c.loop_times > 0 ? m->x0 : nullptr, first_reads_x ? opA : (OT*)nullptr, wp);
     GTB_LAUNCHED();
     bool x_in_opA = first_reads_x;
+    PendingUpdate pend;                       // pre-norm layers: the embedding fills the first copy of the stream only
     for (size_t u = 0; u < m->runs.size(); u++) {
         const Run& run = m->runs[u];
         const LayerW& l = m->L[run.layer];
+        if (l.d.style == GTB_BLOCK_PRENORM) {
+            float* cap_prev = (m->capture && u > 0) ? m->cap + (u - 1) * (size_t)m->max_rows * W : nullptr;
+            int rc = run_prenorm_layer<OT>(m, t, R, S, run, l, portions, pend, cap_prev);
+            if (rc) return rc;
+            if (u + 1 == m->runs.size()) {     // the last update, and the sum of the copies for the output norm
+                rc = hc_boundary<OT>(m, R, pend, nullptr, NormArgs{}, m->x);
+                if (rc) return rc;
+                if (m->capture) {
+                    GTB_CUDA(cudaMemcpyAsync(m->cap + u * (size_t)m->max_rows * W, m->x, (size_t)R * W * sizeof(float), cudaMemcpyDeviceToDevice, st));
+                    m->cap_rows = R;
+                }
+            }
+            continue;
+        }
         if (l.d.style == GTB_BLOCK_POSTNORM) {
             int rc = run_postnorm_layer<OT>(m, t, R, S, run, l, portions, seg_lens, n_qtiles, x_in_opA);
             if (rc) return rc;
@@ -561,11 +734,20 @@ int run_pass(gtb_seq_model* m, const PassTables& t, int R, int S, bool from_pend
         }
     }
     if (n_want > 0) {
-        if (c.final_norm) k_rmsnorm_weight<OT><<<n_want, 256, 0, st>>>(m->x, W, c.eps, m->final_gain, 1, d_want, opH, wp);
+        if (c.final_norm == 2) {
+            NormArgs fn{};
+            fn.kind = GTB_NORM_DYT; fn.w = m->final_gain; fn.b = m->final_b; fn.alpha = m->final_a;
+            k_dyt_rows<OT><<<n_want, 256, 0, st>>>(m->x, W, fn, d_want, opH, wp);
+        } else if (c.final_norm) k_rmsnorm_weight<OT><<<n_want, 256, 0, st>>>(m->x, W, c.eps, m->final_gain, 1, d_want, opH, wp);
         else k_rmsnorm_scalar<OT><<<n_want, 256, 0, st>>>(m->x, W, c.eps, m->final_gain, d_want, opH, wp);
         GTB_LAUNCHED();
         int rc = product<OT>(m, opH, wp, m->head, wp, m->logits, c.vocab, n_want, c.vocab, wp, nullptr, 0);
         if (rc) return rc;
+        if (c.logit_softcap > 0.0f) {
+            const size_t n = (size_t)n_want * c.vocab;
+            k_softcap<<<(unsigned)((n + 255) / 256), 256, 0, st>>>(m->logits, n, c.logit_softcap);
+            GTB_LAUNCHED();
+        }
     }
     k_commit<<<(S + 127) / 128, 128, 0, st>>>(t, S);
     GTB_LAUNCHED();
@@ -610,10 +792,25 @@ int gtb_seq_create(gtb_seq_t* out, const gtb_seq_config* cfg, const gtb_seq_laye
     }
     TRY(dalloc_t(m, &m->head, (size_t)c.vocab * wp));
     want_matrix(m, "head", m->head, c.vocab, W, wp);
-    REQ(c.final_norm == 0 || c.final_norm == 1);
+    REQ(c.final_norm >= 0 && c.final_norm <= 2);
+    REQ(c.streams >= 0 && c.streams <= HC_MAX && c.logit_softcap >= 0.0f);
     TRY(dalloc_t(m, &m->final_gain, c.final_norm ? W : 1));
     if (c.final_norm) want_vector(m, "final.norm", m->final_gain, W, 0);
     else want_vector(m, "final.norm", m->final_gain, 0, 0, true);
+    if (c.final_norm == 2) {
+        TRY(dalloc_t(m, &m->final_b, W));
+        TRY(dalloc_t(m, &m->final_a, 1));
+        want_vector(m, "final.norm.b", m->final_b, W, 0);
+        want_vector(m, "final.norm.alpha", m->final_a, 0, 0, true);
+    }
+    m->ns = c.streams > 0 ? c.streams : 1;
+    m->prenorm = layers[0].style == GTB_BLOCK_PRENORM;
+    if (m->prenorm && c.streams == 0) {
+        TRY(dalloc_t(m, &m->hc_one, 3));
+        const float one[3] = {1.0f, 1.0f, 1.0f};
+        GTB_CUDA(cudaMemcpyAsync(m->hc_one, one, sizeof one, cudaMemcpyHostToDevice, ctx().stream));
+        GTB_CUDA(cudaStreamSynchronize(ctx().stream));
+    }
     if (c.loop_times > 0) {
         TRY(dalloc_t(m, &m->loop_in, (size_t)W * pad64(2 * W)));
         want_matrix(m, "loop.in", m->loop_in, W, 2 * W, pad64(2 * W));
@@ -624,11 +821,14 @@ int gtb_seq_create(gtb_seq_t* out, const gtb_seq_config* cfg, const gtb_seq_laye
     for (int i = 0; i < c.n_layers; i++) {
         LayerW& l = m->L[i];
         l.d = layers[i];
-        const bool post = l.d.style == GTB_BLOCK_POSTNORM;
-        REQ(l.d.style == GTB_BLOCK_PARALLEL || l.d.style == GTB_BLOCK_POSTNORM);
-        REQ(l.d.n_branches >= 1 && l.d.n_branches <= (post ? 1 : 2));
+        const bool post = l.d.style == GTB_BLOCK_POSTNORM, pre = l.d.style == GTB_BLOCK_PRENORM;
+        REQ(l.d.style == GTB_BLOCK_PARALLEL || post || pre);
+        REQ(pre == m->prenorm);                  // the copies of the stream belong to the whole model: pre-norm layers do not mix with the other styles
+        REQ(!pre || (c.loop_times == 0 && c.taps == 0));
+        REQ(l.d.n_branches >= 1 && l.d.n_branches <= (post || pre ? 1 : 2));
         REQ(l.d.ff >= 0);
-        REQ(post ? (l.d.ff == 0 || l.d.ff_kind == GTB_FF_POLYNORM || l.d.ff_kind == GTB_FF_EXPERTS) : l.d.ff_kind == GTB_FF_GEGLU);
+        if (pre) REQ((l.d.norm_kind == GTB_NORM_RMS || l.d.norm_kind == GTB_NORM_DYT) && (l.d.ff == 0 || l.d.ff_kind == GTB_FF_GEGLU || l.d.ff_kind == GTB_FF_GATED_EXPERTS));
+        else REQ(post ? (l.d.ff == 0 || l.d.ff_kind == GTB_FF_POLYNORM || l.d.ff_kind == GTB_FF_EXPERTS) : l.d.ff_kind == GTB_FF_GEGLU);
         l.ff = l.d.ff;
         const std::string lp = "l" + std::to_string(i) + ".";
         int n1 = 0, ko = 0;
@@ -636,7 +836,30 @@ int gtb_seq_create(gtb_seq_t* out, const gtb_seq_config* cfg, const gtb_seq_laye
             BranchW& b = l.br[bi];
             b.d = l.d.branch[bi];
             gtb_seq_branch& d = b.d;
-            REQ(post ? (d.kind == GTB_MIX_MINGRU || d.kind == GTB_MIX_SOFTMAX_ATTN) : (d.kind == GTB_MIX_SIGMOID_ATTN || d.kind == GTB_MIX_RETENTION));
+            REQ(pre ? d.kind == GTB_MIX_LATENT_ATTN : post ? (d.kind == GTB_MIX_MINGRU || d.kind == GTB_MIX_SOFTMAX_ATTN) : (d.kind == GTB_MIX_SIGMOID_ATTN || d.kind == GTB_MIX_RETENTION));
+            if (d.kind == GTB_MIX_LATENT_ATTN) {
+                REQ(d.heads > 0 && d.dim > 0 && d.rope_dim >= 0 && d.vdim > 0 && d.kv_rank > 0 && d.q_rank >= 0 && d.window >= 0);
+                REQ(d.kv_rank <= 512 && d.kv_rank + d.rope_dim <= 1024);        // the absorbed form runs on the row kernels of softmax attention
+                REQ(d.rot_dims >= 0 && d.rot_dims <= d.rope_dim && d.rot_dims % 2 == 0 && (d.gated == 0 || d.gated == 3));
+                d.kv_heads = 1; d.kv_from = -1; d.pool = 0;
+                const int hd = d.dim + d.rope_dim, nq = d.q_rank > 0 ? d.q_rank : d.heads * hd;
+                b.q_off = n1; b.kv_off = n1 + nq; b.g_off = b.kv_off + d.kv_rank + d.rope_dim;
+                n1 = b.g_off + (d.gated ? d.heads : 0);
+                b.a_off = ko; ko += d.heads * d.vdim;
+                b.rank_p = pad64(d.kv_rank); b.qrank_p = d.q_rank > 0 ? pad64(d.q_rank) : 0;
+                b.c_ld = std::max((d.kv_rank + d.rope_dim + 7) / 8 * 8, b.rank_p);
+                if (d.rot_dims > 0) {
+                    b.inv_freq.resize(d.rot_dims / 2);
+                    for (int k = 0; k < d.rot_dims / 2; k++) b.inv_freq[k] = (float)pow((double)d.rot_base, -2.0 * k / d.rot_dims);
+                    TRY(dalloc_t(m, &b.d_inv_freq, b.inv_freq.size()));
+                    GTB_CUDA(cudaMemcpyAsync(b.d_inv_freq, b.inv_freq.data(), b.inv_freq.size() * sizeof(float), cudaMemcpyHostToDevice, ctx().stream));
+                }
+                m->lat_q_max = std::max(m->lat_q_max, d.heads * hd);
+                m->lat_qa_max = std::max(m->lat_qa_max, d.heads * (d.kv_rank + d.rope_dim));
+                m->lat_qr_max = std::max(m->lat_qr_max, b.qrank_p);
+                m->lat_ol_max = std::max(m->lat_ol_max, (d.heads * d.kv_rank + 7) / 8 * 8);
+                continue;
+            }
             if (d.kind == GTB_MIX_MINGRU) {
                 REQ(d.dim > 0);
                 d.heads = d.kv_heads = 1; d.vdim = d.dim; d.rot_dims = 0;
@@ -700,7 +923,7 @@ int gtb_seq_create(gtb_seq_t* out, const gtb_seq_config* cfg, const gtb_seq_laye
         }
         GTB_CUDA(cudaStreamSynchronize(ctx().stream));       // the vectors above are read from members that may move; wait for the copies
         l.n1 = n1;
-        l.kout = post ? ko : ko + l.ff;
+        l.kout = (post || pre) ? ko : ko + l.ff;
         l.kout_p = pad64(l.kout);
         TRY(dalloc_t(m, &l.w_mix, (size_t)n1 * wp));
         TRY(dalloc_t(m, &l.w_out, (size_t)W * l.kout_p));
@@ -716,6 +939,29 @@ int gtb_seq_create(gtb_seq_t* out, const gtb_seq_config* cfg, const gtb_seq_laye
                 want_vector(m, bp + "z.b", l.d_bias + b.q_off, d.dim, 0);
                 want_vector(m, bp + "x.b", l.d_bias + b.k_off, d.dim, 0);
                 want_matrix(m, bp + "o", l.w_out + b.a_off, W, d.dim, l.kout_p);
+                continue;
+            }
+            if (d.kind == GTB_MIX_LATENT_ATTN) {
+                const int hd = d.dim + d.rope_dim;
+                if (d.q_rank > 0) {
+                    want_matrix(m, bp + "dq", l.w_mix + (size_t)b.q_off * wp, d.q_rank, W, wp);
+                    TRY(dalloc_t(m, &b.d_qnorm, d.q_rank));
+                    want_vector(m, bp + "dq.norm", b.d_qnorm, d.q_rank, 0);
+                    TRY(dalloc_t(m, &b.w_uq, (size_t)d.heads * hd * b.qrank_p));
+                    want_matrix(m, bp + "uq", b.w_uq, d.heads * hd, d.q_rank, b.qrank_p);
+                } else {
+                    want_matrix(m, bp + "q", l.w_mix + (size_t)b.q_off * wp, d.heads * hd, W, wp);
+                }
+                want_matrix(m, bp + "dkv", l.w_mix + (size_t)b.kv_off * wp, d.kv_rank + d.rope_dim, W, wp);
+                TRY(dalloc_t(m, &b.d_kvnorm, d.kv_rank));
+                want_vector(m, bp + "dkv.norm", b.d_kvnorm, d.kv_rank, 0);
+                TRY(dalloc_t(m, &b.w_uk, (size_t)d.heads * d.dim * b.rank_p));
+                TRY(dalloc_t(m, &b.w_uv, (size_t)d.heads * d.vdim * b.rank_p));
+                want_matrix(m, bp + "uk", b.w_uk, d.heads * d.dim, d.kv_rank, b.rank_p);
+                want_matrix(m, bp + "uv", b.w_uv, d.heads * d.vdim, d.kv_rank, b.rank_p);
+                if (d.sink) { TRY(dalloc_t(m, &b.d_sink, d.heads)); want_vector(m, bp + "sink", b.d_sink, d.heads, 0); }
+                if (d.gated) want_matrix(m, bp + "g", l.w_mix + (size_t)b.g_off * wp, d.heads, W, wp);
+                want_matrix(m, bp + "o", l.w_out + b.a_off, W, d.heads * d.vdim, l.kout_p);
                 continue;
             }
             want_matrix(m, bp + "q", l.w_mix + (size_t)b.q_off * wp, b.kq, W, wp);
@@ -739,7 +985,78 @@ int gtb_seq_create(gtb_seq_t* out, const gtb_seq_config* cfg, const gtb_seq_laye
                 if (d.sink) { TRY(dalloc_t(m, &b.d_sink, d.heads)); want_vector(m, bp + "sink", b.d_sink, d.heads, 0); }
             }
         }
-        if (post) {
+        if (pre) {
+            const int ns = m->ns;
+            for (int q = 0; q < (l.ff > 0 ? 2 : 1); q++) {
+                const std::string np = lp + (q == 0 ? "norm1" : "norm2"), hp = lp + (q == 0 ? "hc1." : "hc2.");
+                float*& nw = q == 0 ? l.norm1 : l.norm2;
+                TRY(dalloc_t(m, &nw, W));
+                want_vector(m, np, nw, W, 0);
+                if (l.d.norm_kind == GTB_NORM_DYT) {
+                    TRY(dalloc_t(m, &l.nb[q], W));
+                    TRY(dalloc_t(m, &l.na[q], 1));
+                    want_vector(m, np + ".b", l.nb[q], W, 0);
+                    want_vector(m, np + ".alpha", l.na[q], 0, 0, true);
+                }
+                if (c.streams > 0) {
+                    TRY(dalloc_t(m, &l.hc[q], (size_t)ns * (2 + ns)));
+                    want_vector(m, hp + "in", l.hc[q], ns, 0);
+                    want_vector(m, hp + "out", l.hc[q] + ns, ns, 0);
+                    want_vector(m, hp + "mix", l.hc[q] + 2 * ns, ns, ns);
+                } else l.hc[q] = m->hc_one;
+            }
+            if (l.ff > 0) {
+                l.kfp = pad64(l.ff);
+                m->kfp_max = std::max(m->kfp_max, l.kfp);
+                if (l.d.ff_kind == GTB_FF_GEGLU) {
+                    TRY(dalloc_t(m, &l.w_gu, (size_t)2 * l.ff * wp));
+                    TRY(dalloc_t(m, &l.w_down, (size_t)W * l.kfp));
+                    l.gu_inter = l.ff % 32 == 0;
+                    want_matrix(m, lp + "mlp.gate", l.w_gu, l.ff, W, wp);
+                    want_matrix(m, lp + "mlp.up", l.w_gu + (size_t)(l.gu_inter ? 32 : l.ff) * wp, l.ff, W, wp);
+                    if (l.gu_inter)
+                        for (const char* nm : {"mlp.gate", "mlp.up"}) { TensorDest& d = m->tensors[lp + nm]; d.group = 32; d.group_stride = 64; }
+                    want_matrix(m, lp + "mlp.down", l.w_down, W, l.ff, l.kfp);
+                    m->g_cols = std::max(m->g_cols, 2 * l.ff);
+                    m->kout_p_max = std::max(m->kout_p_max, l.kfp);
+                } else {
+                    const int E = l.d.experts;
+                    REQ(E > 0 && E <= 4096 && l.d.identity == 0 && l.d.top > 0 && l.d.top <= E && l.d.top <= 64 && l.d.shared_ff >= 0);
+                    l.sff = l.d.shared_ff;
+                    l.n_out = E + (l.sff > 0 ? 1 : 0);
+                    TRY(dalloc_t(m, &l.w_router, (size_t)l.n_out * wp));
+                    want_matrix(m, lp + "mlp.router", l.w_router, E, W, wp);
+                    if (l.sff > 0) want_matrix(m, lp + "mlp.shared.sg", l.w_router + (size_t)E * wp, 1, W, wp);
+                    TRY(dalloc_t(m, &l.w_up, (size_t)E * 2 * l.ff * wp));
+                    TRY(dalloc_t(m, &l.w_down, (size_t)E * W * l.kfp));
+                    l.e_inter = l.ff % 32 == 0;
+                    for (int e = 0; e < E; e++) {
+                        const std::string ep = lp + "mlp.e" + std::to_string(e) + ".";
+                        bf16* base = l.w_up + (size_t)e * 2 * l.ff * wp;
+                        want_matrix(m, ep + "gate", base, l.ff, W, wp);
+                        want_matrix(m, ep + "up", base + (size_t)(l.e_inter ? 32 : l.ff) * wp, l.ff, W, wp);
+                        if (l.e_inter)
+                            for (const char* nm : {"gate", "up"}) { TensorDest& d = m->tensors[ep + nm]; d.group = 32; d.group_stride = 64; }
+                        want_matrix(m, ep + "down", l.w_down + (size_t)e * W * l.kfp, W, l.ff, l.kfp);
+                    }
+                    m->n_out_max = std::max(m->n_out_max, l.n_out);
+                    m->top_max = std::max(m->top_max, l.d.top);
+                    if (l.sff > 0) {
+                        l.sff_p = pad64(l.sff);
+                        l.sh_inter = l.sff % 32 == 0;
+                        TRY(dalloc_t(m, &l.w_sh_gu, (size_t)2 * l.sff * wp));
+                        TRY(dalloc_t(m, &l.w_sh_down, (size_t)W * l.sff_p));
+                        want_matrix(m, lp + "mlp.shared.gate", l.w_sh_gu, l.sff, W, wp);
+                        want_matrix(m, lp + "mlp.shared.up", l.w_sh_gu + (size_t)(l.sh_inter ? 32 : l.sff) * wp, l.sff, W, wp);
+                        if (l.sh_inter)
+                            for (const char* nm : {"mlp.shared.gate", "mlp.shared.up"}) { TensorDest& d = m->tensors[lp + nm]; d.group = 32; d.group_stride = 64; }
+                        want_matrix(m, lp + "mlp.shared.down", l.w_sh_down, W, l.sff, l.sff_p);
+                        m->g_cols = std::max(m->g_cols, 2 * l.sff);
+                        m->kout_p_max = std::max(m->kout_p_max, l.sff_p);
+                    }
+                }
+            }
+        } else if (post) {
             TRY(dalloc_t(m, &l.norm1, W));
             want_vector(m, lp + "norm1", l.norm1, W, 0);
             if (l.ff > 0) {
@@ -821,7 +1138,11 @@ int gtb_seq_create(gtb_seq_t* out, const gtb_seq_config* cfg, const gtb_seq_laye
         size_t per_slot = 0;
         for (int bi = 0; bi < l.d.n_branches; bi++) {
             const gtb_seq_branch& d = l.br[bi].d;
-            if (d.kind == GTB_MIX_SIGMOID_ATTN || d.kind == GTB_MIX_SOFTMAX_ATTN) {
+            if (d.kind == GTB_MIX_LATENT_ATTN) {
+                const size_t cb = (size_t)c.max_ctx * l.br[bi].c_ld * es;
+                TRY(dalloc(m, &r.kc[bi], cb * c.n_slots));
+                per_slot += cb;
+            } else if (d.kind == GTB_MIX_SIGMOID_ATTN || d.kind == GTB_MIX_SOFTMAX_ATTN) {
                 if (d.kind == GTB_MIX_SOFTMAX_ATTN && d.kv_from >= 0) {
                     // no loop (checked above), so run j is layer j: the source layer's cache, appended to earlier in the same pass
                     r.kc[bi] = m->runs[d.kv_from].kc[0];
@@ -875,6 +1196,7 @@ int gtb_seq_create(gtb_seq_t* out, const gtb_seq_config* cfg, const gtb_seq_laye
         size_t hv = 0;
         for (const LayerW& l : m->L)
             if (l.br[0].d.kind == GTB_MIX_SOFTMAX_ATTN) hv = std::max(hv, (size_t)l.br[0].d.heads * (l.br[0].d.vdim + 2));
+            else if (l.br[0].d.kind == GTB_MIX_LATENT_ATTN) hv = std::max(hv, (size_t)l.br[0].d.heads * (l.br[0].d.kv_rank + 2));
         if (hv > 0 && c.max_ctx > 128) TRY(dalloc_t(m, &m->sattn_part, 32 * SPLIT_MAX_ROWS * hv));
     }
     if (m->n_out_max > 0) {
@@ -899,6 +1221,15 @@ int gtb_seq_create(gtb_seq_t* out, const gtb_seq_config* cfg, const gtb_seq_laye
                 if (l.br[bi].d.kind == GTB_MIX_SIGMOID_ATTN) hv = std::max(hv, l.br[bi].d.heads * l.br[bi].d.vdim);
         m->attn_splits = std::max(1, std::min(32, c.max_ctx / 128));
         if (hv > 0 && m->attn_splits > 1) TRY(dalloc_t(m, &m->attn_part, (size_t)m->attn_splits * SPLIT_MAX_ROWS * hv));
+    }
+    if (m->prenorm) {
+        TRY(dalloc_t(m, &m->xs, (size_t)m->ns * R * W));
+        TRY(dalloc_t(m, &m->Y2, R * W));
+        TRY(dalloc_t(m, &m->shw, R));
+        TRY(dalloc_t(m, &m->latQ, R * std::max(m->lat_q_max, 1)));
+        TRY(dalloc_t(m, &m->latQA, R * std::max(m->lat_qa_max, 1)));
+        TRY(dalloc(m, &m->opQ, R * std::max(m->lat_qr_max, 8) * es));
+        TRY(dalloc(m, &m->opO, R * std::max(m->lat_ol_max, 8) * es));
     }
     TRY(dalloc_t(m, &m->logits, R * c.vocab));
     TRY(dalloc(m, &m->opA, R * wp * es));

@@ -328,8 +328,9 @@ struct SoftAttn {
     const float* inv_freq;       // [rot_dims / 2]
     int window, pool;            // window 0: every earlier token; pool 0: no pooled blocks
     const float* sink;           // [heads] or null
-    int gate;                    // 0: none, 1: silu, 2: logistic
+    int gate;                    // 0: none, 1: silu, 2: logistic, 3: logistic of one number per head (column g_off + head)
     int q_off, k_off, v_off, g_off, a_off;
+    int k_ld, v_ld;              // row strides of the key / value cache in elements; 0: packed (kv_heads * dim, kv_heads * vdim)
     int own_kv;                  // 0: keys and values are another layer's cache (nothing is projected or appended here)
     int max_ctx, max_blocks;
 };
@@ -433,12 +434,12 @@ __device__ __forceinline__ void sattn_sweep(const PassTables& t, const SoftAttn&
     const int g = h / (b.heads / b.kv_heads), slot = t.seg_slot[t.row_seg[r]];
     const float* q = P + (size_t)r * ldp + b.q_off + h * b.dim;
     for (int i = threadIdx.x; i < b.dim; i += blockDim.x) sq[i] = q[i];
-    const size_t kld = (size_t)b.kv_heads * b.dim, vld = (size_t)b.kv_heads * b.vdim;
+    const size_t kld = b.k_ld ? (size_t)b.k_ld : (size_t)b.kv_heads * b.dim, vld = b.v_ld ? (size_t)b.v_ld : (size_t)b.kv_heads * b.vdim;
     const OT* kbase = kc + (size_t)slot * b.max_ctx * kld + (size_t)g * b.dim;
     const OT* vbase = vc + (size_t)slot * b.max_ctx * vld + (size_t)g * b.vdim;
     const float* pkb = pk ? pk + (size_t)slot * b.max_blocks * kld + (size_t)g * b.dim : nullptr;
     const float* pvb = pv ? pv + (size_t)slot * b.max_blocks * vld + (size_t)g * b.vdim : nullptr;
-    const bool kvec = b.dim % 8 == 0;
+    const bool kvec = b.dim % 8 == 0 && kld % 8 == 0;
     __syncthreads();
     for (int n0 = n_lo; n0 < n_hi; n0 += blockDim.x) {
         const int n = n0 + threadIdx.x;
@@ -479,8 +480,8 @@ __device__ __forceinline__ void sattn_store(const SoftAttn& b, const float* __re
         if (c < b.vdim) {
             float o = acc[cc] * inv;
             if (b.gate) {
-                const float gt = P[(size_t)r * ldp + b.g_off + h * b.vdim + c];
-                o *= b.gate == 2 ? sigmoidf_(gt) : gt * sigmoidf_(gt);
+                const float gt = P[(size_t)r * ldp + b.g_off + (b.gate == 3 ? h : h * b.vdim + c)];
+                o *= b.gate >= 2 ? sigmoidf_(gt) : gt * sigmoidf_(gt);
             }
             out[(size_t)r * ld_out + b.a_off + h * b.vdim + c] = cvt<OT>(o);
         }

@@ -45,8 +45,13 @@ def _open_robopel(path: Path, dtype: str, n_slots: int, max_ctx: int, **kw):
     return _open_described(robopel, path, dtype, n_slots, max_ctx, **kw)
 
 
-FAMILIES = {"Reninex": _open_reninex, "Robopel": _open_robopel, "TinyLlama": _open_tinyllama}
-STEPWISE = {"Reninex", "Robopel"}          # families of the layer-list library: slots, portion-wise step function, scheduler
+def _open_nanotar(path: Path, dtype: str, n_slots: int, max_ctx: int, **kw):
+    from . import nanotar
+    return _open_described(nanotar, path, dtype, n_slots, max_ctx, **kw)
+
+
+FAMILIES = {"Nanotar": _open_nanotar, "Reninex": _open_reninex, "Robopel": _open_robopel, "TinyLlama": _open_tinyllama}
+STEPWISE = {"Nanotar", "Reninex", "Robopel"}          # families of the layer-list library: slots, portion-wise step function, scheduler
 
 
 def family_of(path) -> str:

@@ -12,9 +12,10 @@ HERE = Path(__file__).resolve().parent
 LIB_PATH = HERE / "libgten_b200_seq.so"
 
 BF16, F32 = 0, 1
-MIX_SIGMOID_ATTN, MIX_RETENTION, MIX_MINGRU, MIX_SOFTMAX_ATTN = 1, 2, 3, 4
-BLOCK_PARALLEL, BLOCK_POSTNORM = 0, 1
-FF_GEGLU, FF_POLYNORM, FF_EXPERTS = 0, 1, 2
+MIX_SIGMOID_ATTN, MIX_RETENTION, MIX_MINGRU, MIX_SOFTMAX_ATTN, MIX_LATENT_ATTN = 1, 2, 3, 4, 5
+BLOCK_PARALLEL, BLOCK_POSTNORM, BLOCK_PRENORM = 0, 1, 2
+FF_GEGLU, FF_POLYNORM, FF_EXPERTS, FF_GATED_EXPERTS = 0, 1, 2, 3
+NORM_RMS, NORM_DYT = 0, 1
 ROT_HALVES, ROT_INTERLEAVED = 0, 1
 MODE_BY_NAME = {"bfloat16": BF16, "bf16": BF16, "float32": F32, "fp32": F32}
 
@@ -28,18 +29,20 @@ class BranchC(C.Structure):
                 ("scale", C.c_float), ("qk_norm", C.c_int), ("rot_dims", C.c_int), ("rot_base", C.c_float), ("out_norm", C.c_int),
                 ("gated", C.c_int), ("out_scale", C.c_float), ("decay", C.POINTER(C.c_float)), ("rot_layout", C.c_int),
                 ("rot_factor", C.c_float), ("rot_low", C.c_float), ("rot_high", C.c_float), ("rot_original", C.c_float), ("softcap", C.c_float),
-                ("window", C.c_int), ("pool", C.c_int), ("sink", C.c_int), ("kv_from", C.c_int)]
+                ("window", C.c_int), ("pool", C.c_int), ("sink", C.c_int), ("kv_from", C.c_int),
+                ("rope_dim", C.c_int), ("kv_rank", C.c_int), ("q_rank", C.c_int)]
 
 
 class LayerC(C.Structure):
     _fields_ = [("n_branches", C.c_int), ("branch", BranchC * 2), ("ff", C.c_int), ("style", C.c_int), ("ff_kind", C.c_int),
-                ("experts", C.c_int), ("top", C.c_int), ("identity", C.c_int)]
+                ("experts", C.c_int), ("top", C.c_int), ("identity", C.c_int), ("norm_kind", C.c_int), ("shared_ff", C.c_int)]
 
 
 class ConfigC(C.Structure):
     _fields_ = [(n, C.c_int) for n in ("vocab", "width", "n_layers")] + [("eps", C.c_float)] + \
                [(n, C.c_int) for n in ("taps", "bigram_buckets", "bigram_mul_prev", "bigram_mul_cur", "loop_start", "loop_stop", "loop_times",
-                                       "mode", "n_slots", "max_ctx", "max_rows")] + [("embed_scale", C.c_float), ("final_norm", C.c_int)]
+                                       "mode", "n_slots", "max_ctx", "max_rows")] + [("embed_scale", C.c_float), ("final_norm", C.c_int), ("streams", C.c_int),
+                                                                                     ("logit_softcap", C.c_float)]
 
 
 SYMBOLS = ["gtb_seq_create", "gtb_seq_destroy", "gtb_seq_set_tensor", "gtb_seq_finalize", "gtb_seq_n_runs", "gtb_seq_slot_reset",
@@ -122,7 +125,7 @@ class SeqModel:
     """A described model resident on the GPU: weights, n_slots sequences of state, the step function."""
 
     def __init__(self, desc: dict, mode: int, n_slots: int, max_ctx: int, max_rows: int = 0):
-        """desc: the flat description a model family's config reader produces (see reninex.describe, robopel.describe)."""
+        """desc: the flat description a model family's config reader produces (see reninex.describe, robopel.describe, nanotar.describe)."""
         self.desc, self.mode, self.n_slots, self.max_ctx = desc, mode, n_slots, max_ctx
         self.vocab, self.width = desc["vocab"], desc["width"]
         layers = (LayerC * len(desc["layers"]))()
@@ -132,6 +135,7 @@ class SeqModel:
             lc.ff = l["ff"]
             lc.style, lc.ff_kind = l.get("style", BLOCK_PARALLEL), l.get("ff_kind", FF_GEGLU)
             lc.experts, lc.top, lc.identity = l.get("experts", 0), l.get("top", 0), l.get("identity", 0)
+            lc.norm_kind, lc.shared_ff = l.get("norm_kind", NORM_RMS), l.get("shared_ff", 0)
             for bc, b in zip(lc.branch, l["branches"]):
                 bc.kind, bc.name = b["kind"], b["name"].encode()
                 bc.heads, bc.kv_heads, bc.dim, bc.vdim = b["heads"], b.get("kv_heads", b["heads"]), b["dim"], b["vdim"]
@@ -142,6 +146,7 @@ class SeqModel:
                 bc.rot_factor, bc.rot_low, bc.rot_high, bc.rot_original = (b.get("rot_" + k, 0.0) for k in ("factor", "low", "high", "original"))
                 bc.softcap, bc.window, bc.pool = b.get("softcap", 0.0), b.get("window", 0), b.get("pool", 0)
                 bc.sink, bc.kv_from = int(b.get("sink", 0)), b.get("kv_from", -1)
+                bc.rope_dim, bc.kv_rank, bc.q_rank = b.get("rope_dim", 0), b.get("kv_rank", 0), b.get("q_rank", 0)
                 if b.get("decay") is not None:
                     arr = (C.c_float * len(b["decay"]))(*b["decay"])
                     self._keep.append(arr)
@@ -150,7 +155,7 @@ class SeqModel:
         cfg = ConfigC(desc["vocab"], desc["width"], len(desc["layers"]), desc["eps"], desc.get("taps", 0),
                       bg["buckets"] if bg else 0, bg["mul_prev"] if bg else 0, bg["mul_cur"] if bg else 0,
                       lp["start"] if lp else 0, lp["stop"] if lp else 0, lp["times"] if lp else 0, mode, n_slots, max_ctx, max_rows,
-                      desc.get("embed_scale", 1.0), int(desc.get("final_norm", 0)))
+                      desc.get("embed_scale", 1.0), int(desc.get("final_norm", 0)), int(desc.get("streams", 0)), float(desc.get("logit_softcap", 0.0)))
         self.h = C.c_void_p()
         check(lib().gtb_seq_create(C.byref(self.h), C.byref(cfg), layers))
         n = C.c_int()
