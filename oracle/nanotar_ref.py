@@ -58,8 +58,9 @@ def softmax_with_sink(scores, sink):
     return e / den
 
 
-def latent_attention(h, T, mx, eps, first_pos=0):
-    """h [T, width] -> [T, width].  T: tensors of the mixer by their short names; mx: the layer's `mixer` section."""
+def latent_attention(h, T, mx, eps, first_pos=0, book=None):
+    """h [T, width] -> [T, width].  T: tensors of the mixer by their short names; mx: the layer's `mixer` section.
+    book: a list that receives (query position, head, first visible key, softmax weights of the visible keys)."""
     H, dn, dr, dv, rank = mx["heads"], mx["dim"], mx["rot_dim"], mx["vdim"], mx["kv_rank"]
     n = h.shape[0]
     pos = np.arange(first_pos, first_pos + n)
@@ -71,7 +72,7 @@ def latent_attention(h, T, mx, eps, first_pos=0):
     q = q.reshape(n, H, dn + dr)
     dkv = h @ T["dkv"].T
     c = unit_rms(dkv[:, :rank], eps) * T["dkv.norm"]
-    rot = mx["rot"]
+    rot = mx.get("rot") or {"dims": 0, "base": 1.0}
     k_rot = rotate_pairs(dkv[:, rank:], pos, rot["dims"], rot["base"])                    # [n, dr], one for all heads
     q_rot = rotate_pairs(q[:, :, dn:], pos, rot["dims"], rot["base"])
     k_plain = (c @ T["uk"].T).reshape(n, H, dn)
@@ -84,6 +85,8 @@ def latent_attention(h, T, mx, eps, first_pos=0):
         for a in range(H):
             s = (k_plain[lo:i + 1, a] @ q[i, a, :dn] + k_rot[lo:i + 1] @ q_rot[i, a]) * mx["scale"]
             w = softmax_with_sink(s, T["sink"][a] if "sink" in T else None)
+            if book is not None:
+                book.append((i, a, lo, w))
             out[i, a] = (w @ val[lo:i + 1, a]) * gate[i, a]
     return out.reshape(n, H * dv) @ T["o"].T
 
@@ -128,7 +131,12 @@ def hyper_update(xs, hc, f):
     return np.tensordot(hc["mix"].T, xs, axes=(1, 0)) + hc["out"][:, None, None] * y[None]
 
 
-def forward(cfg, tensors, tokens, layer_outputs=None):
+def to_float(bits):
+    """bfloat16 bit patterns -> float64"""
+    return (np.asarray(bits, np.uint16).astype(np.uint32) << 16).view(np.float32).astype(np.float64)
+
+
+def forward(cfg, tensors, tokens, layer_outputs=None, book=None):
     """tokens -> logits [T, vocab] of a whole sequence from position 0.  tensors: name -> float64 array.
     layer_outputs: a list that receives the sum of the streams after every layer."""
     eps = cfg["norm"]["eps"]
@@ -137,7 +145,10 @@ def forward(cfg, tensors, tokens, layer_outputs=None):
     for i, lay in enumerate(cfg["layers"]):
         p = f"l{i}."
         n1 = lambda v: dyt(v, tensors[p + "norm1.alpha"], tensors[p + "norm1"], tensors[p + "norm1.b"])
-        xs = hyper_update(xs, sub(tensors, p + "hc1."), lambda u: latent_attention(n1(u), sub(tensors, p + "mix."), lay["mixer"], eps))
+        bk = [] if book is not None else None
+        xs = hyper_update(xs, sub(tensors, p + "hc1."), lambda u: latent_attention(n1(u), sub(tensors, p + "mix."), lay["mixer"], eps, book=bk))
+        if book is not None:
+            book.append(bk)
         if lay.get("mlp"):
             n2 = lambda v: dyt(v, tensors[p + "norm2.alpha"], tensors[p + "norm2"], tensors[p + "norm2.b"])
             xs = hyper_update(xs, sub(tensors, p + "hc2."), lambda u: feed_forward(n2(u), sub(tensors, p + "mlp."), lay["mlp"]))

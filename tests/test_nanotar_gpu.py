@@ -1,0 +1,543 @@
+"""The Nanotar family on the layer-list library (libgten_b200_seq.so) against the plain numpy restatement in oracle/nanotar_ref.py.
+
+Every test makes its own small configuration and random weights.  float32 mode is held to rounding (1e-4 of the logits' spread);
+bfloat16 mode to a loose bound that a wrong key, window edge, sink or expert still breaks by orders of magnitude.  Where random
+weights would hide a fault (one far key among hundreds, a window's edge, the sink) the test plants a key: one input channel marks
+the needle token and one the query token, a large weight carries the first into the latent and the second into head 0's query,
+and the restatement confirms that this key takes the query's attention."""
+import json
+
+import numpy as np
+import pytest
+
+pytestmark = pytest.mark.gpu
+
+from oracle import nanotar_ref as R  # noqa: E402
+from tinyllama_cpp_b200 import nanotar as NT  # noqa: E402
+from tinyllama_cpp_b200 import safetensors_io as st  # noqa: E402
+
+
+@pytest.fixture(scope="module")
+def lib():
+    from tinyllama_cpp_b200 import build, seq
+    build.build(target="seq")
+    seq.init(0)
+    return seq
+
+
+def make(lib, cfg, mode="float32", seed=0, n_slots=3, max_ctx=512, max_rows=0, tweak=None, **synth):
+    desc = NT.describe(cfg)
+    t = NT.synth_tensors(desc, seed, **synth)
+    if tweak:
+        tweak(t)
+    m = lib.SeqModel(desc, lib.MODE_BY_NAME[mode], n_slots, max_ctx, max_rows).load(t)
+    return m, {k: R.to_float(v) for k, v in t.items()}
+
+
+def rel(got, want):
+    """rms of the difference after removing each row's mean, over the rms spread of the expected rows."""
+    d = got - want
+    d = d - d.mean(-1, keepdims=True)
+    w = want - want.mean(-1, keepdims=True)
+    return float(np.sqrt((d * d).mean(-1)).max() / np.sqrt((w * w).mean()))
+
+
+TOL = {"float32": 1e-4, "bfloat16": 6e-2}
+
+
+def close(got, want, mode, cfg=None):
+    """Within TOL on every row -- except bfloat16 runs of models with routed experts: operand rounding may flip a close choice between
+    two experts at a few tokens (a flipped token is then off by its whole expert, and colours the rows after it), so there nine rows
+    in ten are held to TOL and the rest only to being of the logits' own size."""
+    routed = cfg is not None and any((l.get("mlp") or {}).get("kind") == "moe" for l in cfg["layers"])
+    if mode != "bfloat16" or not routed:
+        return rel(got, want) < TOL[mode]
+    d = got - want
+    d = d - d.mean(-1, keepdims=True)
+    w = want - want.mean(-1, keepdims=True)
+    rows = np.sqrt((d * d).mean(-1)) / np.sqrt((w * w).mean())
+    return float(np.mean(rows < TOL[mode])) >= 0.9 and float(rows.max()) < 2.0
+
+
+def toks(seed, n, vocab, lo=0):
+    return np.random.default_rng(1000 + seed).integers(lo, vocab, n).astype(np.int32)
+
+
+L, D, E = NT.latent_layer, NT.dense_mlp, NT.moe_mlp
+
+
+# ------------------------------------------------------------------ each mechanism alone
+VARIANTS = {
+    "causal": (2, [L()]),
+    "causal_dense": (2, [L(mlp=D(56))]),
+    "one_stream": (1, [L(mlp=D(40)), L(heads=2)]),
+    "five_streams": (5, [L(mlp=D(40)), L(mlp=D(24))]),
+    "no_rotated_part": (2, [L(rot_dim=0, mlp=D(40))]),
+    "partly_rotated": (2, [L(rot_dim=12, rot_dims=6, rot_base=300.0)]),
+    "query_latent_window_sink": (2, [L(heads=4, dim=6, rot_dim=8, vdim=10, kv_rank=24, q_rank=12, window=9)]),
+    "window_of_one": (3, [L(q_rank=8, window=1, mlp=D(32))]),
+    "experts": (2, [L(mlp=E(experts=5, top=2, ff=24, shared_ff=0))]),
+    "experts_shared": (2, [L(mlp=E(experts=7, top=3, ff=16, shared_ff=40))]),
+    "experts_top1": (2, [L(mlp=E(experts=4, top=1, ff=8, shared_ff=8))]),
+    "experts_all_chosen": (2, [L(mlp=E(experts=3, top=3, ff=32, shared_ff=32))]),
+    "all": (3, None),
+}
+
+
+@pytest.mark.parametrize("mode", ["float32", "bfloat16"])
+@pytest.mark.parametrize("variant", list(VARIANTS))
+def test_mechanisms_one_at_a_time(lib, mode, variant):
+    streams, layers = VARIANTS[variant]
+    cfg = NT.make_config(vocab=101, width=72, streams=streams, layers=layers)
+    m, W = make(lib, cfg, mode, seed=3)
+    m.set_option("capture", 1)
+    t = toks(1, 41, cfg["vocab"])
+    got = m.step([(0, t)], range(len(t)))
+    trace = []
+    want = R.forward(cfg, W, t, trace)
+    assert m.n_runs == len(trace)
+    for u in range(m.n_runs):            # the sum of the stream's copies after every layer, first and last row
+        for r in (0, len(t) - 1):
+            assert rel(m.read_capture(u, r)[None], trace[u][r][None]) < TOL[mode] * (4 if mode == "bfloat16" else 1), (u, r)
+    assert close(got, want, mode, cfg), rel(got, want)
+
+
+def test_restatement_guards():
+    """Guards the restatement: softmax weights and the sink's share, the window's first key, renormalised router weights, a
+    hyper-connection with identity weights is a plain residual sum, rotation keeps lengths and composes."""
+    rng = np.random.default_rng(0)
+    s = rng.standard_normal(7)
+    w = R.softmax_with_sink(s, 0.3)
+    assert np.isclose(w.sum(), np.exp(s).sum() / (np.exp(s).sum() + np.exp(0.3))) and np.isclose(R.softmax_with_sink(s, None).sum(), 1.0)
+    assert [R.visible(i, 4) for i in (0, 3, 4, 9)] == [0, 0, 1, 6] and R.visible(9, 0) == 0
+    idx, wt = R.route(rng.standard_normal((5, 8)), rng.standard_normal((6, 8)), 3)
+    assert idx.shape == (5, 3) and np.allclose(wt.sum(-1), 1.0) and np.all(np.diff(wt, axis=-1) <= 0)
+    xs = rng.standard_normal((3, 4, 5))
+    out = R.hyper_update(xs, {"in": np.ones(3) / 3, "out": np.ones(3), "mix": np.eye(3)}, lambda u: 2.0 * u)
+    assert np.allclose(out, xs + 2.0 * xs.mean(0))
+    v = rng.standard_normal((6, 2, 8))
+    r1 = R.rotate_pairs(v, np.arange(6), 4, 100.0)
+    assert np.allclose(np.linalg.norm(r1, axis=-1), np.linalg.norm(v, axis=-1)) and np.allclose(r1[..., 4:], v[..., 4:]) and np.allclose(r1[0], v[0])
+    assert np.allclose(R.rotate_pairs(r1, np.arange(6), 4, 100.0), R.rotate_pairs(v, 2 * np.arange(6), 4, 100.0))
+
+
+# ------------------------------------------------------------------ prefill = decode = portions
+@pytest.mark.parametrize("mode", ["float32", "bfloat16"])
+def test_prefill_against_token_by_token(lib, mode):
+    cfg = NT.make_config(vocab=90, width=64)
+    m, W = make(lib, cfg, mode, seed=5)
+    t = toks(2, 70, cfg["vocab"])
+    whole = m.step([(0, t)], range(len(t)))
+    one = np.concatenate([m.step([(1, t[i:i + 1])], [0]) for i in range(len(t))])
+    want = R.forward(cfg, W, t)
+    assert close(whole, want, mode, cfg) and close(one, want, mode, cfg) and close(one, whole, mode, cfg)
+
+
+@pytest.mark.parametrize("mode", ["float32", "bfloat16"])
+@pytest.mark.parametrize("sizes", [[2, 2, 2, 3, 50, 2, 7, 1, 1, 30], [33, 1, 64, 2], [97, 3], [1] * 5 + [95], [70, 30]])
+def test_portions_of_any_size(lib, mode, sizes):
+    layers = [L(heads=4, dim=8, rot_dim=8, vdim=24, kv_rank=32, q_rank=24, window=13, mlp=E(experts=5, top=2, ff=32, shared_ff=32)), L(mlp=D(64)),
+              L(heads=2, dim=16, rot_dim=8, vdim=8, kv_rank=16, q_rank=8, window=29)]
+    cfg = NT.make_config(vocab=77, width=48, layers=layers)
+    m, W = make(lib, cfg, mode, seed=7)
+    n = sum(sizes)
+    t = toks(3, n, cfg["vocab"])
+    want = R.forward(cfg, W, t)
+    at, rows = 0, []
+    for s in sizes:
+        rows.append(m.step([(2, t[at:at + s])], range(s)))
+        at += s
+    assert m.position(2) == n
+    assert close(np.concatenate(rows), want, mode, cfg)
+
+
+def test_passes_inside_a_step_cut_anywhere(lib):
+    """max_rows smaller than a step: the library cuts the step into passes; same logits."""
+    cfg = NT.make_config(vocab=64, width=64)
+    t = toks(4, 70, 64)
+    m1, W = make(lib, cfg, "float32", seed=9, max_rows=16)
+    m2, _ = make(lib, cfg, "float32", seed=9)
+    a = m1.step([(0, t), (1, t[:23])], range(93))
+    b = m2.step([(0, t), (1, t[:23])], range(93))
+    assert rel(a[:70], R.forward(cfg, W, t)) < TOL["float32"] and rel(a, b) < 1e-5
+
+
+# ------------------------------------------------------------------ batches, slots
+@pytest.mark.parametrize("mode", ["float32", "bfloat16"])
+def test_batch_of_unequal_requests_equals_each_alone(lib, mode):
+    cfg = NT.make_config(vocab=80, width=64)
+    m, W = make(lib, cfg, mode, seed=11, n_slots=4)
+    seqs = [toks(10 + i, n, 80) for i, n in enumerate((67, 5, 94, 1))]
+    first = [s[: max(1, len(s) // 2)] for s in seqs]
+    out1 = m.step([(i, f) for i, f in enumerate(first)], range(sum(len(f) for f in first)))
+    rest = [(i, s[len(f):]) for i, (s, f) in enumerate(zip(seqs, first)) if len(s) > len(f)]
+    out2 = m.step(rest, range(sum(len(r) for _, r in rest)))
+    at1, at2 = 0, 0
+    for i, (s, f) in enumerate(zip(seqs, first)):
+        want = R.forward(cfg, W, s)
+        got = out1[at1:at1 + len(f)]
+        at1 += len(f)
+        if len(s) > len(f):
+            got = np.concatenate([got, out2[at2:at2 + len(s) - len(f)]])
+            at2 += len(s) - len(f)
+        assert close(got, want, mode, cfg), i
+
+
+def test_slot_freed_and_used_again(lib):
+    from tinyllama_cpp_b200.scheduler import SlotManager
+    cfg = NT.make_config(vocab=70, width=64)
+    m, W = make(lib, cfg, "float32", seed=13, n_slots=2)
+    sm = SlotManager(m)
+    a, b, c = toks(20, 60, 70), toks(21, 9, 70), toks(22, 45, 70)
+    sa = sm.acquire("a")
+    m.step([(sa, a)])
+    sb = sm.acquire("b")
+    m.step([(sb, b[:4])])
+    sm.release("a")
+    sc = sm.acquire("c")                 # takes a's slot: a's cached latents must not show
+    assert sc == sa
+    got_c = m.step([(sc, c), (sb, b[4:])], range(len(c) + len(b) - 4))
+    assert rel(got_c[: len(c)], R.forward(cfg, W, c)) < TOL["float32"]
+    assert rel(got_c[len(c):], R.forward(cfg, W, b)[4:]) < TOL["float32"]
+    with pytest.raises(RuntimeError):
+        sm.acquire("d")
+
+
+# ------------------------------------------------------------------ planted keys: window edges, far keys, the sink
+NEEDLE, QUERY, C_NEEDLE, C_QUERY = 1, 2, 5, 9
+
+
+def planted(lib, window, mode="float32", max_ctx=700, sink=None, heads=2):
+    """One latent-attention layer without a feed-forward.  Channel C_NEEDLE of the embedding is non-zero for token NEEDLE only and
+    C_QUERY for token QUERY only (large: the norm's tanh saturates); a large weight carries the first into entry 0 of the latent
+    and, through uk, into head 0's plain key entry 0, and the second into the same entry of head 0's query.  Filler tokens are
+    3 .. vocab-1.  window = 0: the causal form; else the form with a query latent, a window and a sink."""
+    lay = L(heads=heads, dim=8, rot_dim=4, vdim=12, kv_rank=16, scale=1.0) if not window else L(heads=heads, dim=8, rot_dim=4, vdim=12, kv_rank=16, q_rank=8, window=window, scale=1.0)
+    cfg = NT.make_config(vocab=60, width=40, streams=2, layers=[lay])
+
+    def put(t, name, fn):
+        a = st.bf16_bits_to_f32(t[name]).astype(np.float64)
+        fn(a)
+        t[name] = st.f32_to_bf16_bits(a.astype(np.float32))
+
+    def tweak(t):
+        def emb(a):
+            a[:, C_NEEDLE] = 0.0
+            a[:, C_QUERY] = 0.0
+            a[NEEDLE, C_NEEDLE] = 40.0
+            a[QUERY, C_QUERY] = 40.0
+        put(t, "embed", emb)
+        put(t, "l0.norm1.b", lambda a: a.__setitem__([C_NEEDLE, C_QUERY], 0.0))
+        put(t, "l0.norm1", lambda a: a.__setitem__([C_NEEDLE, C_QUERY], 1.0))
+        put(t, "l0.hc1.in", lambda a: a.__setitem__(slice(None), 0.5))
+        put(t, "l0.mix.dkv", lambda a: (a.__setitem__((slice(None), C_NEEDLE), 0.0), a.__setitem__((0, C_NEEDLE), 30.0)))
+        put(t, "l0.mix.dkv.norm", lambda a: a.__setitem__(0, 1.0))
+        put(t, "l0.mix.uk", lambda a: (a.__setitem__((slice(None), 0), 0.0), a.__setitem__((0, 0), 3.0)))
+        if window:
+            put(t, "l0.mix.dq", lambda a: (a.__setitem__((slice(None), C_QUERY), 0.0), a.__setitem__((0, C_QUERY), 30.0)))
+            put(t, "l0.mix.dq.norm", lambda a: a.__setitem__(0, 1.0))
+            put(t, "l0.mix.uq", lambda a: (a.__setitem__((slice(None), 0), 0.0), a.__setitem__((0, 0), 3.0)))
+            put(t, "l0.mix.sink", lambda a: a.__setitem__(slice(None), -4.0 if sink is None else sink))
+        else:
+            put(t, "l0.mix.q", lambda a: (a.__setitem__((slice(None), C_QUERY), 0.0), a.__setitem__((0, C_QUERY), 8.0)))
+    return cfg, make(lib, cfg, mode, seed=17, max_ctx=max_ctx, tweak=tweak)
+
+
+def needle_weight(cfg, W, t):
+    """Share of the last query's attention (head 0) that lands on needle tokens, by the restatement."""
+    book = []
+    R.forward(cfg, W, t, book=book)
+    i, a, lo, w = [b for b in book[0] if b[0] == len(t) - 1 and b[1] == 0][0]
+    return float(sum(w[j - lo] for j in range(lo, i + 1) if t[j] == NEEDLE))
+
+
+def run_three_ways(m, t):
+    """The last token's logits: whole prompt, decoded alone after the rest, and in portions of changing size."""
+    n = len(t)
+    whole = m.step([(0, t)], [n - 1])
+    m.step([(1, t[:-1])])
+    dec = m.step([(1, t[-1:])], [0])
+    at, sizes = 0, [2, 37, 3, 64, 2, 5]
+    while at < n - 1:
+        s = min(sizes[0], n - 1 - at)
+        sizes = sizes[1:] + sizes[:1]
+        m.step([(2, t[at:at + s])])
+        at += s
+    por = m.step([(2, t[-1:])], [0])
+    for s in range(3):
+        m.reset(s)
+    return whole, dec, por
+
+
+@pytest.mark.parametrize("mode", ["float32", "bfloat16"])
+@pytest.mark.parametrize("window,n", [(21, 90), (64, 200), (1, 40), (130, 300)])
+def test_window_edge_in_prompt_and_decode(lib, mode, window, n):
+    """A needle exactly `window - 1` tokens back is seen, one token further it is not."""
+    cfg, (m, W) = planted(lib, window, mode)
+    seen = {}
+    for back in (window - 1, window):
+        t = toks(30, n, 60, lo=3)
+        t[-1] = QUERY
+        if back > 0:
+            t[n - 1 - back] = NEEDLE
+        seen[back] = needle_weight(cfg, W, t)
+        want = R.forward(cfg, W, t)[-1:]
+        for got in run_three_ways(m, t):
+            assert rel(got, want) < TOL[mode], back
+    if window > 1:
+        assert seen[window - 1] > 0.5
+    assert seen[window] == 0.0
+
+
+@pytest.mark.parametrize("mode", ["float32", "bfloat16"])
+def test_far_key_among_hundreds(lib, mode):
+    """The causal form: one needle hundreds of tokens back carries the last query; without it the answer moves."""
+    n = 640
+    cfg, (m, W) = planted(lib, 0, mode)
+    t = toks(32, n, 60, lo=3)
+    t[-1], t[7] = QUERY, NEEDLE
+    assert needle_weight(cfg, W, t) > 0.5
+    want = R.forward(cfg, W, t)[-1:]
+    for got in run_three_ways(m, t):
+        assert rel(got, want) < TOL[mode]
+    t2 = t.copy()
+    t2[7] = 7
+    assert rel(R.forward(cfg, W, t2)[-1:], want) > 50 * TOL["float32"]
+
+
+def test_sink_counts_once_and_has_no_value(lib):
+    """A sink far above every score takes nearly all of the softmax: the mixer's output shrinks towards nothing.  The restatement
+    agrees at both ends, and the two ends differ."""
+    outs = {}
+    for sink in (-30.0, 12.0):
+        cfg, (m, W) = planted(lib, 16, "float32", sink=sink)
+        t = toks(33, 50, 60, lo=3)
+        want = R.forward(cfg, W, t)
+        assert rel(m.step([(0, t)], range(50)), want) < TOL["float32"]
+        assert rel(np.concatenate([m.step([(1, t[i:i + 1])], [0]) for i in range(50)]), want) < TOL["float32"]
+        outs[sink] = want
+    assert rel(outs[-30.0], outs[12.0]) > 100 * TOL["float32"]
+
+
+@pytest.mark.parametrize("n", [63, 64, 65, 127, 128, 129, 257])
+def test_key_tile_borders_in_prompt_and_decode(lib, n):
+    cfg = NT.make_config(vocab=64, width=64, layers=[L(), L(q_rank=16, window=150, mlp=D(32))])
+    for mode in ("float32", "bfloat16"):
+        m, W = make(lib, cfg, mode, seed=19)
+        t = toks(30, n + 2, 64)
+        want = R.forward(cfg, W, t)
+        got = m.step([(0, t[:n])], [n - 2, n - 1])
+        got = np.concatenate([got, m.step([(0, t[n:n + 1])], [0]), m.step([(0, t[n + 1:])], [0])])
+        assert rel(got, want[n - 2:]) < TOL[mode]
+
+
+def test_first_tokens(lib):
+    """Positions 0 .. a few: one key beside the sink, a window that is not yet full."""
+    cfg = NT.make_config(vocab=50, width=64, layers=[L(mlp=E()), L(q_rank=8, window=4, mlp=D()), L(q_rank=8, window=3)])
+    m, W = make(lib, cfg, "float32", seed=23)
+    t = toks(40, 11, 50)
+    want = R.forward(cfg, W, t)
+    assert rel(m.step([(0, t)], range(11)), want) < TOL["float32"]
+    got = np.concatenate([m.step([(1, t[i:i + 1])], [0]) for i in range(11)])
+    assert rel(got, want) < TOL["float32"]
+
+
+# ------------------------------------------------------------------ long decoding, other sizes
+@pytest.mark.parametrize("mode", ["float32", "bfloat16"])
+def test_long_decoding(lib, mode):
+    """The windows move over decoded tokens for 250 steps; the causal layers keep every latent."""
+    cfg = NT.make_config(vocab=64, width=64, layers=[L(mlp=D()), L(q_rank=16, window=40, mlp=E()), L(q_rank=8, window=17), L(heads=1)])
+    m, W = make(lib, cfg, mode, seed=29)
+    t = toks(50, 260, 64)
+    want = R.forward(cfg, W, t)
+    m.step([(0, t[:10])])
+    got = np.concatenate([m.step([(0, t[i:i + 1])], [0]) for i in range(10, 260)])
+    assert close(got, want[10:], mode, cfg)
+    assert close(got[-25:], want[-25:], mode, cfg)
+
+
+@pytest.mark.parametrize("streams,layers,vocab,width", [
+    (1, [L(heads=1, dim=40, rot_dim=2, vdim=8, kv_rank=9, mlp=D(24)), L(heads=3, dim=5, rot_dim=6, vdim=7, kv_rank=11, q_rank=13, window=50, mlp=E(3, 3, 8, 8))], 33, 40),
+    (4, [L(heads=8, dim=8, rot_dim=8, vdim=24, kv_rank=64, mlp=E(9, 4, 40, 72)), L(heads=2, dim=24, rot_dim=16, vdim=40, kv_rank=48, q_rank=80, window=6, mlp=E(2, 1, 72, 0))], 130, 136),
+    (2, [L(heads=2, dim=120, rot_dim=16, vdim=136, kv_rank=72, mlp=D(32))], 64, 64),                      # heads beyond the tiled kernel's sizes
+    (2, [L(heads=4, dim=20, rot_dim=12, rot_dims=4, vdim=12, kv_rank=20, q_rank=20, window=1), L(heads=2, dim=20, rot_dim=12, vdim=12, kv_rank=20, q_rank=12, window=64)], 64, 64),
+    (8, [L(heads=3, dim=10, rot_dim=10, vdim=10, kv_rank=30, mlp=E(3, 1, 10, 10)), L(heads=3, dim=20, rot_dim=2, vdim=10, kv_rank=25, q_rank=7, window=9, mlp=D(30))], 37, 50),
+])
+def test_other_sizes(lib, streams, layers, vocab, width):
+    cfg = NT.make_config(vocab=vocab, width=width, streams=streams, layers=layers, eps=3e-4, logit_softcap=3.0)
+    for mode in ("float32", "bfloat16"):
+        m, W = make(lib, cfg, mode, seed=31)
+        t = toks(60, 85, vocab)
+        want = R.forward(cfg, W, t)
+        got = np.concatenate([m.step([(0, t[:20])], range(20)), m.step([(0, t[20:22])], range(2)), m.step([(0, t[22:])], range(63))])
+        assert close(got, want, mode, cfg), (mode, rel(got, want))
+
+
+def test_logits_without_a_soft_cap(lib):
+    cfg = NT.make_config(vocab=64, width=64, logit_softcap=0.0)
+    m, W = make(lib, cfg, "float32", seed=37)
+    t = toks(61, 30, 64)
+    want = R.forward(cfg, W, t)
+    assert rel(m.step([(0, t)], range(30)), want) < TOL["float32"]
+    capped = R.forward(dict(cfg, logit_softcap=0.5), W, t)
+    assert np.abs(capped).max() <= 0.5 and rel(capped, want) > 100 * TOL["float32"]
+
+
+@pytest.mark.parametrize("mode", ["float32", "bfloat16"])
+@pytest.mark.parametrize("layers", [
+    [L(heads=4, dim=16, rot_dim=16, vdim=16, kv_rank=40, mlp=E(6, 2, 32, 32)), L(heads=2, dim=24, rot_dim=8, vdim=48, kv_rank=32, q_rank=24, window=40, mlp=D(64))],
+    [L(heads=2, dim=48, rot_dim=16, vdim=40, kv_rank=64, q_rank=32, window=100), L(heads=4, dim=48, rot_dim=16, vdim=40, kv_rank=24, q_rank=48, window=70, mlp=E(3, 2, 64, 0))],
+    [L(heads=3, dim=20, rot_dim=12, vdim=12, kv_rank=36), L(heads=2, dim=96, rot_dim=32, vdim=128, kv_rank=128, mlp=E(12, 3, 96, 64))],
+])
+def test_tiled_kernels_on_portions(lib, mode, layers):
+    """Prompt portions run the tiled path (keys and values expanded from the cached latents for the tensor-core attention, grouped
+    expert products in bfloat16 mode): portions that start in the middle of a sequence and end inside a tile, passes of several
+    segments -- against the restatement and against the row kernels (options fused_attn = 0, grouped_experts = 0)."""
+    cfg = NT.make_config(vocab=64, width=64, layers=layers)
+    m, W = make(lib, cfg, mode, seed=61, n_slots=4, max_ctx=400)
+    a, b = toks(110, 300, 64), toks(111, 170, 64)
+    wa, wb = R.forward(cfg, W, a), R.forward(cfg, W, b)
+    outs = {}
+    for fused in (1, 0):
+        m.set_option("fused_attn", fused)
+        m.set_option("grouped_experts", fused)
+        sa, sb = (0, 1) if fused else (2, 3)
+        g1 = m.step([(sa, a[:70])], range(70))
+        g2 = m.step([(sa, a[70:199]), (sb, b[:33])], range(129 + 33))
+        g3 = m.step([(sb, b[33:170]), (sa, a[199:300])], range(137 + 101))
+        ga = np.concatenate([g1, g2[:129], g3[137:]])
+        gb = np.concatenate([g2[129:], g3[:137]])
+        assert close(ga, wa, mode, cfg) and close(gb, wb, mode, cfg), (fused, rel(ga, wa), rel(gb, wb))
+        outs[fused] = (ga, gb)
+    assert close(outs[1][0], outs[0][0], mode, cfg) and close(outs[1][1], outs[0][1], mode, cfg)
+    nxt = m.step([(0, [5])], [0])            # decoding continues from the cache the tiled path left
+    assert rel(nxt, R.forward(cfg, W, np.append(a, 5))[-1:]) < (TOL[mode] if mode == "float32" else 2.0)
+
+
+def test_tensor_core_path_with_awkward_sizes(lib):
+    """bfloat16 mode, portions of 64 rows and more: the tcgen05 products (fused gate-times-up epilogues, grouped experts) and the
+    tiled attention with sizes that are multiples of nothing, against the SIMT kernels."""
+    cfg = NT.make_config(vocab=101, width=72, streams=3, layers=[L(heads=6, dim=12, rot_dim=6, vdim=20, kv_rank=50, mlp=E(5, 2, 32, 64)),
+                                                                  L(heads=3, dim=20, rot_dim=10, vdim=10, kv_rank=44, q_rank=30, window=40, mlp=D(96))])
+    m, W = make(lib, cfg, "bfloat16", seed=67)
+    t = toks(120, 150, cfg["vocab"])
+    want = R.forward(cfg, W, t)
+    got = np.concatenate([m.step([(0, t[:70])], range(70)), m.step([(0, t[70:])], range(80))])
+    assert close(got, want, "bfloat16", cfg)
+    m.set_option("tensor", 0)
+    simt = np.concatenate([m.step([(1, t[:70])], range(70)), m.step([(1, t[70:])], range(80))])
+    assert close(got, simt, "bfloat16", cfg)
+
+
+def test_router_renormalises_and_ties_go_to_the_lower_index(lib):
+    """Two experts with identical router rows tie at every token: the lower index is chosen.  Weights are the chosen scores over their sum."""
+    cfg = NT.make_config(vocab=40, width=32, streams=2, layers=[L(mlp=E(experts=4, top=1, ff=16, shared_ff=0))])
+
+    def tweak(t):
+        r = st.bf16_bits_to_f32(t["l0.mlp.router"]).copy()
+        r[2] = r[1] = np.abs(r[1]) * 4.0        # experts 1 and 2 share a row
+        t["l0.mlp.router"] = st.f32_to_bf16_bits(r)
+    m, W = make(lib, cfg, "float32", seed=71, tweak=tweak)
+    t = toks(7, 30, 40)
+    want = R.forward(cfg, W, t)
+    assert rel(m.step([(0, t)], range(30)), want) < TOL["float32"]
+    other = dict(W)
+    other["l0.mlp.e1.down"], other["l0.mlp.e2.down"] = W["l0.mlp.e2.down"], W["l0.mlp.e1.down"]
+    assert rel(R.forward(cfg, other, t), want) > 50 * TOL["float32"]          # choosing expert 2 at the ties would show
+
+
+# ------------------------------------------------------------------ generation through the scheduler, command line
+def oracle_greedy(cfg, W, prompt, n_new):
+    t = list(prompt)
+    margins = []
+    for _ in range(n_new):
+        lg = R.forward(cfg, W, t)[-1]
+        o = np.argsort(lg)
+        margins.append(lg[o[-1]] - lg[o[-2]])
+        t.append(int(o[-1]))
+    return np.asarray(t[len(prompt):]), np.asarray(margins)
+
+
+def test_greedy_generation_through_the_scheduler(lib):
+    from tinyllama_cpp_b200.scheduler import generate
+    cfg = NT.make_config(vocab=64, width=64)
+    m, W = make(lib, cfg, "float32", seed=41, n_slots=2, gain=2.0)
+    prompts = [toks(80 + i, n, 64) for i, n in enumerate((19, 3, 40))]     # three requests, two slots: one waits
+    outs = generate(m, prompts, 12, chunk=8, burst=5)
+    for p, o in zip(prompts, outs):
+        want, margin = oracle_greedy(cfg, W, p, 12)
+        assert len(o) == 12
+        k = int(np.argmax(o != want)) if np.any(o != want) else 12
+        assert k == 12 or margin[k] < 1e-3, (o, want, margin)
+
+
+def test_device_decode_loop_equals_host_fed_steps(lib):
+    cfg = NT.make_config(vocab=64, width=64)
+    m, _ = make(lib, cfg, "float32", seed=43, n_slots=3, gain=2.0)
+    p0, p1 = toks(90, 11, 64), toks(91, 30, 64)
+    nxt = m.step_greedy([(0, p0), (1, p1)])
+    dev = m.decode([0, 1], 9)
+    m.set_option("graph", 0)
+    m.reset(0), m.reset(1)
+    assert np.array_equal(nxt, m.step_greedy([(0, p0), (1, p1)]))
+    assert np.array_equal(dev, m.decode([0, 1], 9))
+    m.reset(2)
+    cur, host = int(m.step_greedy([(2, p1)])[0]), []
+    for _ in range(9):
+        cur = int(m.step_greedy([(2, [cur])])[0])
+        host.append(cur)
+    assert host == dev[1].tolist()
+    assert m.position(1) == 30 + 9
+
+
+def test_missing_and_misshapen_tensors_are_named(lib):
+    cfg = NT.make_config(vocab=64, width=64)
+    d = NT.describe(cfg)
+    t = NT.synth_tensors(d, 0)
+    t.pop("l1.mix.sink")
+    with pytest.raises(lib.SeqError, match="l1.mix.sink"):
+        lib.SeqModel(d, lib.F32, 1, 16).load(t)
+    t = NT.synth_tensors(d, 0)
+    t["l0.hc2.mix"] = t["l0.hc2.mix"][:2]
+    with pytest.raises(lib.SeqError, match="l0.hc2.mix"):
+        lib.SeqModel(d, lib.F32, 1, 16).load(t)
+    t = NT.synth_tensors(d, 0)
+    t["l0.mix.sink"] = t["l1.mix.sink"]                # the causal form has no sink
+    with pytest.raises(lib.SeqError, match="l0.mix.sink"):
+        lib.SeqModel(d, lib.F32, 1, 16).load(t)
+
+
+def test_command_line_generation_and_trace_replay(lib, tmp_path):
+    """bin/generate and bin/trace_run on a checkpoint folder written by the family's own writer."""
+    import subprocess
+    import sys
+    from pathlib import Path
+    root = Path(__file__).resolve().parent.parent
+    cfg = NT.make_config(vocab=64, width=64, layers=[L(mlp=D()), L(q_rank=16, window=8, heads=2, vdim=8, mlp=D(32)), L()])      # (no routed experts: bfloat16 is held to TOL below)
+    t = NT.synth_tensors(NT.describe(cfg), 71, gain=2.0)
+    NT.write_checkpoint(tmp_path / "m", cfg, t)
+    W = {k: R.to_float(v) for k, v in t.items()}
+    p = toks(130, 37, 64)
+    out = subprocess.run([sys.executable, str(root / "bin" / "generate"), "--model", str(tmp_path / "m"), "--dtype", "float32", "--prompt",
+                          ",".join(map(str, p)), "--max-new", "6", "--chunk", "8"], capture_output=True, text=True, timeout=300)
+    assert out.returncode == 0, out.stderr[-2000:]
+    got = np.array([int(x) for x in out.stdout.strip().splitlines()[-1].split(",")])
+    want, margin = oracle_greedy(cfg, W, p, 6)
+    k = int(np.argmax(got != want)) if np.any(got != want) else 6
+    assert k == 6 or margin[k] < 1e-3
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": p[:29].tolist(), "want": [28, 2]}], "end": []},
+             {"step": 1, "entries": [{"id": "a", "tokens": p[29:].tolist(), "want": []}], "end": []},
+             {"step": 2, "entries": [{"id": "a", "tokens": [9], "want": [0]}], "end": ["a"]},
+             {"step": 3, "entries": [{"id": "b", "tokens": p[:3].tolist(), "want": [2]}], "end": ["b"]}]
+    for dtype in ("bfloat16", "float32"):
+        o = tmp_path / ("o_" + dtype)
+        tr = subprocess.run([str(root / "bin" / "trace_run"), "--model", str(tmp_path / "m"), "--dtype", dtype, "--out", str(o), "--max-tokens", "64"],
+                            input="\n".join(json.dumps(x) for x in steps) + "\n", capture_output=True, text=True, timeout=300)
+        assert tr.returncode == 0, tr.stderr[-2000:]
+        assert [l for l in tr.stdout.splitlines() if l.startswith("done")] == [f"done {i}" for i in range(4)]
+        lg = R.forward(cfg, W, np.append(p, 9))
+        tol = TOL[dtype] if dtype == "float32" else 2.0 * TOL[dtype]
+        assert rel(np.fromfile(o / "0.f32", "<f4").reshape(2, 64), lg[[28, 2]]) < tol      # in the order asked for
+        assert not (o / "1.f32").exists()
+        assert rel(np.fromfile(o / "2.f32", "<f4").reshape(1, 64), lg[37:38]) < tol
+        assert rel(np.fromfile(o / "3.f32", "<f4").reshape(1, 64), lg[2:3]) < tol

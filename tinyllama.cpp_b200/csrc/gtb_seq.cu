@@ -116,6 +116,9 @@ struct gtb_seq_model {
     bool prenorm = false;
     float *xs = nullptr, *hc_one = nullptr, *latQ = nullptr, *latQA = nullptr, *Y2 = nullptr, *shw = nullptr;
     void *opQ = nullptr, *opO = nullptr;
+    float* latX = nullptr;                       // expanded [plain keys | values] of one segment's visible range, fp32 [max_ctx][heads * (dim + vdim)]
+    bf16 *latKx = nullptr, *latVx = nullptr;     // the same as bf16 heads [n_slots][max_ctx][heads][dim + rope | vdim], shared by the layers
+    int lat_kx_max = 0, lat_vx_max = 0, lat_x_max = 0;
     int lat_q_max = 0, lat_qa_max = 0, lat_qr_max = 0, lat_ol_max = 0;
     // workspace of a pass
     int max_rows = 0, n1_max = 0, ff_max = 0, kout_p_max = 0, ro_max = 0;
@@ -442,7 +445,11 @@ int run_postnorm_layer(gtb_seq_model* m, const PassTables& t, int R, int S, cons
 
 // ---- pre-norm layers ---------------------------------------------------------------------------------------------------------
 // a finished sublayer whose update of the stream copies has not been applied yet
-struct PendingUpdate { const float* Y = nullptr; const float* Y2 = nullptr; const float* hc = nullptr; int src_ns = 1; };
+struct PendingUpdate {
+    const float* Y = nullptr;  const float* Y2 = nullptr;             // the sublayer's output (Y2: a second share, the shared expert)
+    const float* Yg = nullptr; const int* pair_dst = nullptr; int top = 0;   // grouped experts: rows of Yg to sum instead of Y
+    const float* hc = nullptr; int src_ns = 1;
+};
 
 NormArgs norm_args(const gtb_seq_model* m, const LayerW& l, int q) {
     NormArgs n{};
@@ -453,7 +460,7 @@ NormArgs norm_args(const gtb_seq_model* m, const LayerW& l, int q) {
 template <typename OT>
 int hc_boundary(gtb_seq_model* m, int R, PendingUpdate& pend, const float* hc_next, const NormArgs& nrm, float* xsum) {
     const int W = m->cfg.width;
-    k_hc_step<OT><<<R, 256, 0, ctx().stream>>>(m->xs, (size_t)m->max_rows * W, m->ns, pend.src_ns, W, pend.Y, pend.Y2, pend.hc, hc_next, nrm, (OT*)m->opA, m->wp, xsum);
+    k_hc_step<OT><<<R, 256, 0, ctx().stream>>>(m->xs, (size_t)m->max_rows * W, m->ns, pend.src_ns, W, pend.Y, pend.Y2, pend.Yg, pend.pair_dst, pend.top, pend.hc, hc_next, nrm, (OT*)m->opA, m->wp, xsum);
     GTB_LAUNCHED();
     pend = PendingUpdate{};
     pend.src_ns = m->ns;
@@ -479,7 +486,8 @@ SoftAttn lat_soft_args(const gtb_seq_model* m, const BranchW& b) {
 // One pre-norm layer on R rows.  pend carries the update of the sublayer before it (none for the first layer) and leaves with this
 // layer's last sublayer pending; cap_prev: where the sum of the copies after the previous layer goes (capture), or null.
 template <typename OT>
-int run_prenorm_layer(gtb_seq_model* m, const PassTables& t, int R, int S, const Run& run, const LayerW& l, bool portions, PendingUpdate& pend, float* cap_prev) {
+int run_prenorm_layer(gtb_seq_model* m, const PassTables& t, int R, int S, const Run& run, const LayerW& l, bool portions, const int* seg_lens, const int* seg_slots,
+                      int n_qtiles, PendingUpdate& pend, float* cap_prev) {
     cudaStream_t st = ctx().stream;
     const gtb_seq_config& c = m->cfg;
     const int W = c.width, wp = m->wp;
@@ -489,6 +497,9 @@ int run_prenorm_layer(gtb_seq_model* m, const PassTables& t, int R, int S, const
     rc = product<OT>(m, opA, wp, l.w_mix, wp, m->P, l.n1, R, l.n1, wp, nullptr, 0);
     if (rc) return rc;
     const BranchW& b = l.br[0];
+    // prompt portions in bf16 mode: keys and values of the visible range are expanded from the cached latents and the heads run the
+    // tensor-core softmax attention; everything else runs the absorbed form on the row kernels
+    const bool expand = portions && sizeof(OT) == 2 && seg_slots && m->latKx && b.d.dim + b.d.rope_dim <= 128 && b.d.vdim <= 128;
     {
         const LatAttn a = lat_args(m, b);
         const int hd = a.dim + a.rope;
@@ -497,10 +508,37 @@ int run_prenorm_layer(gtb_seq_model* m, const PassTables& t, int R, int S, const
         const float* Q = m->P;
         int ldq = l.n1, q0 = b.q_off;
         if (a.q_rank > 0) {
-            rc = product<OT>(m, m->opQ, b.qrank_p, b.w_uq, b.qrank_p, m->latQ, a.heads * hd, R, a.heads * hd, b.qrank_p, nullptr, 0);
+            ldq = a.heads * hd + a.heads;         // room for the heads' gate logits behind the queries (the tiled path reads them there)
+            rc = product<OT>(m, m->opQ, b.qrank_p, b.w_uq, b.qrank_p, m->latQ, ldq, R, a.heads * hd, b.qrank_p, nullptr, 0);
             if (rc) return rc;
-            Q = m->latQ; ldq = a.heads * hd; q0 = 0;
+            Q = m->latQ; q0 = 0;
         }
+        if (expand) {
+            const int ld_qr = a.heads * hd + a.heads, nx = a.heads * (a.dim + a.vdim);
+            k_lat_qrot<<<R, 128, 0, st>>>(t, a, Q, ldq, q0, m->P, l.n1, m->latQ, ld_qr);
+            GTB_LAUNCHED();
+            for (int s = 0; s < S; s++) {
+                const int slot = seg_slots[s], p0 = m->host_pos[slot];
+                const int lo = b.d.window > 0 ? std::max(0, p0 - b.d.window + 1) : 0, n = p0 + seg_lens[s] - lo;
+                const bf16* src = (const bf16*)run.kc[0] + ((size_t)slot * c.max_ctx + lo) * b.c_ld;
+                rc = product<OT>(m, src, b.c_ld, b.w_uk, b.rank_p, m->latX, nx, n, nx, b.rank_p, nullptr, 0);      // uk and uv rows are one matrix
+                if (rc) return rc;
+                k_lat_pack<<<n, 256, 0, st>>>(a, m->latX, n, slot, lo, (const bf16*)run.kc[0], m->latKx, m->latVx);
+                GTB_LAUNCHED();
+            }
+            SoftAttn sa{};
+            sa.heads = sa.kv_heads = a.heads; sa.dim = hd; sa.vdim = a.vdim; sa.scale = b.d.scale; sa.eps = c.eps; sa.window = b.d.window; sa.sink = b.d_sink;
+            sa.gate = b.d.gated; sa.q_off = 0; sa.g_off = a.heads * hd; sa.a_off = b.a_off; sa.own_kv = 1; sa.max_ctx = c.max_ctx;
+            rc = sattn_mma(t, sa, S, n_qtiles, m->latQ, ld_qr, m->latKx, m->latVx, nullptr, nullptr, (bf16*)opC, l.kout_p);
+            if (rc > 0) return rc;
+            if (rc < 0) return gtb::fail(GTB_ERR_STATE, "head sizes outside the tiled attention kernel");
+        }
+    }
+    if (!expand) {
+        const LatAttn a = lat_args(m, b);
+        const int hd = a.dim + a.rope;
+        const float* Q = a.q_rank > 0 ? m->latQ : m->P;
+        const int ldq = a.q_rank > 0 ? a.heads * hd + a.heads : l.n1, q0 = a.q_rank > 0 ? 0 : b.q_off;
         k_lat_qabs<<<dim3(R, a.heads), 128, hd * sizeof(float), st>>>(t, a, Q, ldq, q0, b.w_uk, b.rank_p, m->latQA);
         GTB_LAUNCHED();
         const SoftAttn sa = lat_soft_args(m, b);
@@ -558,13 +596,37 @@ int run_prenorm_layer(gtb_seq_model* m, const PassTables& t, int R, int S, const
     k_moe_route_sigmoid<<<R, 32, E * sizeof(float), st>>>(m->rl, l.n_out, E, top, m->sel_idx, m->sel_w, l.sff > 0 ? m->shw : nullptr);
     GTB_LAUNCHED();
     if (l.sff > 0) {
-        rc = product<OT>(m, opA, wp, l.w_sh_gu, wp, m->G, 2 * l.sff, R, 2 * l.sff, wp, nullptr, 0);
-        if (rc) return rc;
-        k_swiglu_rows<OT><<<R, 256, 0, st>>>(m->G, l.sff, l.sh_inter ? 1 : 0, m->shw, opC, l.sff_p);
-        GTB_LAUNCHED();
+        bool act_done = false;
+        if (sizeof(OT) == 2 && m->use_tensor && m->gp && R >= m->tensor_min_rows && l.sh_inter) {
+            rc = seq_gemm_bf16_gated(m->gp, opA, wp, l.w_sh_gu, wp, opC, l.sff_p, 0, R, 2 * l.sff, wp, 1, m->shw);
+            if (rc > 0) return rc;
+            if (rc == 0) { ctx().launches++; act_done = true; }
+        }
+        if (!act_done) {
+            rc = product<OT>(m, opA, wp, l.w_sh_gu, wp, m->G, 2 * l.sff, R, 2 * l.sff, wp, nullptr, 0);
+            if (rc) return rc;
+            k_swiglu_rows<OT><<<R, 256, 0, st>>>(m->G, l.sff, l.sh_inter ? 1 : 0, m->shw, opC, l.sff_p);
+            GTB_LAUNCHED();
+        }
         rc = product<OT>(m, opC, l.sff_p, l.w_sh_down, l.sff_p, m->Y2, W, R, W, l.sff_p, nullptr, 0);
         if (rc) return rc;
         pend.Y2 = m->Y2;
+    }
+    const int n_pairs = R * top, mpad = (n_pairs + 127) / 128 * 128 + E * 128;
+    if (sizeof(OT) == 2 && m->grouped_experts && m->use_tensor && m->gp && m->Xg && l.e_inter && R >= m->tensor_min_rows && mpad <= m->mpad_max) {
+        // rows sorted by expert; the gate-and-up product writes w * silu(gate) * up per (row, choice), the down product one output row per pair,
+        // and the next boundary sums a row's pairs
+        k_moe_group<<<1, 1024, 2 * E * sizeof(int), st>>>(m->sel_idx, n_pairs, E, m->pair_dst, m->tile_e, mpad / 128);
+        GTB_LAUNCHED();
+        k_moe_gather<<<n_pairs, 128, 0, st>>>((const bf16*)opA, wp, top, m->pair_dst, m->sel_w, m->Xg, m->rw);
+        GTB_LAUNCHED();
+        rc = seq_gemm_bf16_grouped_gated(m->gp, m->Xg, wp, l.w_up, wp, mpad, 2 * l.ff, wp, E, m->tile_e, m->actg, l.kfp, m->rw, 1);
+        if (rc == 0) rc = seq_gemm_bf16_grouped(m->gp, m->actg, l.kfp, l.w_down, l.kfp, mpad, W, l.kfp, E, m->tile_e, m->Yg, W, nullptr, 0, nullptr);
+        if (rc > 0) return rc;
+        if (rc == 0) {
+            pend.Yg = m->Yg; pend.pair_dst = m->pair_dst; pend.top = top; pend.hc = l.hc[1];
+            return GTB_OK;
+        }
     }
     {
         const int cta_budget = std::max(1, 4096 / std::max(1, R * top));
@@ -579,7 +641,8 @@ int run_prenorm_layer(gtb_seq_model* m, const PassTables& t, int R, int S, const
 
 // the launch sequence of one pass: R rows of S segments whose tables are already on the device
 template <typename OT>
-int run_pass(gtb_seq_model* m, const PassTables& t, int R, int S, bool from_pending, int n_want, const int* d_want, const int* seg_lens = nullptr) {
+int run_pass(gtb_seq_model* m, const PassTables& t, int R, int S, bool from_pending, int n_want, const int* d_want, const int* seg_lens = nullptr,
+             const int* seg_slots = nullptr) {
     cudaStream_t st = ctx().stream;
     const gtb_seq_config& c = m->cfg;
     const int W = c.width, wp = m->wp;
@@ -601,7 +664,7 @@ int run_pass(gtb_seq_model* m, const PassTables& t, int R, int S, bool from_pend
         const LayerW& l = m->L[run.layer];
         if (l.d.style == GTB_BLOCK_PRENORM) {
             float* cap_prev = (m->capture && u > 0) ? m->cap + (u - 1) * (size_t)m->max_rows * W : nullptr;
-            int rc = run_prenorm_layer<OT>(m, t, R, S, run, l, portions, pend, cap_prev);
+            int rc = run_prenorm_layer<OT>(m, t, R, S, run, l, portions, seg_lens, seg_slots, n_qtiles, pend, cap_prev);
             if (rc) return rc;
             if (u + 1 == m->runs.size()) {     // the last update, and the sum of the copies for the output norm
                 rc = hc_boundary<OT>(m, R, pend, nullptr, NormArgs{}, m->x);
@@ -854,7 +917,12 @@ int gtb_seq_create(gtb_seq_t* out, const gtb_seq_config* cfg, const gtb_seq_laye
                     TRY(dalloc_t(m, &b.d_inv_freq, b.inv_freq.size()));
                     GTB_CUDA(cudaMemcpyAsync(b.d_inv_freq, b.inv_freq.data(), b.inv_freq.size() * sizeof(float), cudaMemcpyHostToDevice, ctx().stream));
                 }
-                m->lat_q_max = std::max(m->lat_q_max, d.heads * hd);
+                m->lat_q_max = std::max(m->lat_q_max, d.heads * hd + d.heads);
+                if (hd <= 128 && d.vdim <= 128) {
+                    m->lat_kx_max = std::max(m->lat_kx_max, d.heads * hd);
+                    m->lat_vx_max = std::max(m->lat_vx_max, d.heads * d.vdim);
+                    m->lat_x_max = std::max(m->lat_x_max, d.heads * (d.dim + d.vdim));
+                }
                 m->lat_qa_max = std::max(m->lat_qa_max, d.heads * (d.kv_rank + d.rope_dim));
                 m->lat_qr_max = std::max(m->lat_qr_max, b.qrank_p);
                 m->lat_ol_max = std::max(m->lat_ol_max, (d.heads * d.kv_rank + 7) / 8 * 8);
@@ -955,8 +1023,8 @@ int gtb_seq_create(gtb_seq_t* out, const gtb_seq_config* cfg, const gtb_seq_laye
                 want_matrix(m, bp + "dkv", l.w_mix + (size_t)b.kv_off * wp, d.kv_rank + d.rope_dim, W, wp);
                 TRY(dalloc_t(m, &b.d_kvnorm, d.kv_rank));
                 want_vector(m, bp + "dkv.norm", b.d_kvnorm, d.kv_rank, 0);
-                TRY(dalloc_t(m, &b.w_uk, (size_t)d.heads * d.dim * b.rank_p));
-                TRY(dalloc_t(m, &b.w_uv, (size_t)d.heads * d.vdim * b.rank_p));
+                TRY(dalloc_t(m, &b.w_uk, (size_t)d.heads * (d.dim + d.vdim) * b.rank_p));      // uv follows uk: one product expands keys and values
+                b.w_uv = b.w_uk + (size_t)d.heads * d.dim * b.rank_p;
                 want_matrix(m, bp + "uk", b.w_uk, d.heads * d.dim, d.kv_rank, b.rank_p);
                 want_matrix(m, bp + "uv", b.w_uv, d.heads * d.vdim, d.kv_rank, b.rank_p);
                 if (d.sink) { TRY(dalloc_t(m, &b.d_sink, d.heads)); want_vector(m, bp + "sink", b.d_sink, d.heads, 0); }
@@ -1041,6 +1109,7 @@ int gtb_seq_create(gtb_seq_t* out, const gtb_seq_config* cfg, const gtb_seq_laye
                     }
                     m->n_out_max = std::max(m->n_out_max, l.n_out);
                     m->top_max = std::max(m->top_max, l.d.top);
+                    m->e_max = std::max(m->e_max, E);
                     if (l.sff > 0) {
                         l.sff_p = pad64(l.sff);
                         l.sh_inter = l.sff % 32 == 0;
@@ -1230,6 +1299,11 @@ int gtb_seq_create(gtb_seq_t* out, const gtb_seq_config* cfg, const gtb_seq_laye
         TRY(dalloc_t(m, &m->latQA, R * std::max(m->lat_qa_max, 1)));
         TRY(dalloc(m, &m->opQ, R * std::max(m->lat_qr_max, 8) * es));
         TRY(dalloc(m, &m->opO, R * std::max(m->lat_ol_max, 8) * es));
+        if (c.mode == GTB_SEQ_BF16 && m->lat_kx_max > 0) {
+            TRY(dalloc_t(m, &m->latX, (size_t)c.max_ctx * m->lat_x_max));
+            TRY(dalloc_t(m, &m->latKx, (size_t)c.n_slots * c.max_ctx * m->lat_kx_max));
+            TRY(dalloc_t(m, &m->latVx, (size_t)c.n_slots * c.max_ctx * m->lat_vx_max));
+        }
     }
     TRY(dalloc_t(m, &m->logits, R * c.vocab));
     TRY(dalloc(m, &m->opA, R * wp * es));
@@ -1399,8 +1473,8 @@ static int step_impl(gtb_seq_t m, int n_seg, const int32_t* seg_slot, const int3
         int rc;
         // greedy passes: logits rows are ordered like greedy_segs; the argmax kernel needs a segment per logits row, so it runs on
         // a table of its own below
-        if (c.mode == GTB_SEQ_F32) rc = run_pass<float>(m, t, R, S, false, nw, d_want, pl.data());
-        else rc = run_pass<bf16>(m, t, R, S, false, nw, d_want, pl.data());
+        if (c.mode == GTB_SEQ_F32) rc = run_pass<float>(m, t, R, S, false, nw, d_want, pl.data(), ps.data());
+        else rc = run_pass<bf16>(m, t, R, S, false, nw, d_want, pl.data(), ps.data());
         if (rc) return rc;
         if (greedy && nw) {
             // segment table restricted to the segments that ended: reuse the upload buffer behind the pass's tables

@@ -53,7 +53,8 @@ struct SqEpi {
     int* status;
     const int* tile_group;   // grouped product: group of every M tile (-1: skip), or null
     int group_rows;          // rows of W per group
-    const float* row_w;      // EPI_RELU2: weight of every row of A
+    const float* row_w;      // EPI_RELU2: weight of every row of A; EPI_GEGLU: optional weight of every row
+    int act_kind;            // EPI_GEGLU: 0 = gelu_tanh(gate) * up, 1 = silu(gate) * up
 };
 
 // bounded wait: false when the barrier did not complete (or another role gave up)
@@ -73,6 +74,10 @@ __device__ __forceinline__ float sq_gelu(float z) {
     asm("tanh.approx.f32 %0, %1;" : "=f"(th) : "f"(c * (z + 0.044715f * z * z * z)));
     return 0.5f * z * (1.0f + th);
 }
+
+// silu(z) = z / (1 + 2^(-z log2 e)) on the special-function unit; the value is rounded to bf16 right after
+__device__ __forceinline__ float sq_silu(float z) { return __fdividef(z, 1.0f + __expf(-z)); }
+__device__ __forceinline__ float sq_gate(float z, int kind) { return kind ? sq_silu(z) : sq_gelu(z); }
 
 template <int BN, int EPI>
 __global__ void __launch_bounds__(SQ_THREADS, 1)
@@ -225,6 +230,8 @@ k_seq_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUte
                 }
             } else {
                 // 64 accumulator columns = 32 gate columns followed by their 32 up columns
+                const float wt = (ep.row_w && row < M) ? ep.row_w[row] : 1.0f;
+                const int ak = ep.act_kind;
 #pragma unroll 1
                 for (int c2 = chalf * (BN / 128); c2 < (chalf + 1) * (BN / 128); c2++) {
                     const int col = nt * BN + c2 * 64;
@@ -241,7 +248,7 @@ k_seq_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUte
                                 uint32_t w[4];
 #pragma unroll
                                 for (int q = 0; q < 4; q++) {
-                                    const __nv_bfloat162 v = __floats2bfloat162_rn(sq_gelu(g[j + 2 * q]) * u[j + 2 * q], sq_gelu(g[j + 2 * q + 1]) * u[j + 2 * q + 1]);
+                                    const __nv_bfloat162 v = __floats2bfloat162_rn(wt * sq_gate(g[j + 2 * q], ak) * u[j + 2 * q], wt * sq_gate(g[j + 2 * q + 1], ak) * u[j + 2 * q + 1]);
                                     w[q] = *reinterpret_cast<const uint32_t*>(&v);
                                 }
                                 *reinterpret_cast<uint4*>(dst + j) = make_uint4(w[0], w[1], w[2], w[3]);
@@ -249,7 +256,7 @@ k_seq_gemm(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUte
                         } else {
 #pragma unroll
                             for (int j = 0; j < 32; j++)
-                                if (j < nc) dst[j] = __float2bfloat16_rn(sq_gelu(g[j]) * u[j]);
+                                if (j < nc) dst[j] = __float2bfloat16_rn(wt * sq_gate(g[j], ak) * u[j]);
                         }
                     }
                 }
@@ -367,10 +374,32 @@ int seq_gemm_bf16_grouped(SeqGemmPlan* p, const void* A, int lda, const void* W,
 }
 
 int seq_gemm_bf16_geglu(SeqGemmPlan* p, const void* A, int lda, const void* W, int ldw, void* act, int ld_act, int act_off, int M, int N2, int K) {
+    return seq_gemm_bf16_gated(p, A, lda, W, ldw, act, ld_act, act_off, M, N2, K, 0, nullptr);
+}
+
+int seq_gemm_bf16_gated(SeqGemmPlan* p, const void* A, int lda, const void* W, int ldw, void* act, int ld_act, int act_off, int M, int N2, int K, int act_kind,
+                        const float* row_w) {
     if (N2 % 64) return -1;                      // whole (32 gate, 32 up) groups only
     SqEpi ep{};
     ep.act = reinterpret_cast<__nv_bfloat16*>(act); ep.ld_act = ld_act; ep.act_off = act_off; ep.status = p ? p->d_status : nullptr;
+    ep.act_kind = act_kind; ep.row_w = row_w;
     return run(p, SQ_EPI_GEGLU, A, lda, W, ldw, M, N2, K, ep);
+}
+
+int seq_gemm_bf16_grouped_gated(SeqGemmPlan* p, const void* A, int lda, const void* W, int ldw, int M_pad, int N2, int K, int n_groups, const int* tile_group,
+                                void* act, int ld_act, const float* row_w, int act_kind) {
+    if (!p || K <= 0 || (K % SQ_BK) || (lda % 8) || (ldw % 8) || (((uintptr_t)A | (uintptr_t)W) & 15) || (M_pad % SQ_BM) || n_groups <= 0 || (N2 % 64) || !act) return -1;
+    SqEpi ep{};
+    ep.act = reinterpret_cast<__nv_bfloat16*>(act); ep.ld_act = ld_act; ep.status = p->d_status;
+    ep.tile_group = tile_group; ep.group_rows = N2; ep.row_w = row_w; ep.act_kind = act_kind;
+    const int mt = M_pad / SQ_BM;
+    const int bn = (N2 > 128 && mt * ((N2 + 255) / 256) * 2 >= ctx().sm_count) ? 256 : 128;
+    CUtensorMap ta, tb;
+    int rc = make_map(p, &ta, A, M_pad, K, lda, SQ_BM);
+    if (rc) return rc;
+    rc = make_map(p, &tb, W, n_groups * N2, K, ldw, bn);
+    if (rc) return rc;
+    return bn == 256 ? launch<256, SQ_EPI_GEGLU>(p, ta, tb, M_pad, N2, K, ep) : launch<128, SQ_EPI_GEGLU>(p, ta, tb, M_pad, N2, K, ep);
 }
 
 }  // namespace seq

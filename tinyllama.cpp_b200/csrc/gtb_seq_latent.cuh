@@ -28,16 +28,20 @@ __device__ __forceinline__ float silu_(float z) { return z * sigmoidf_(z); }
 // One kernel per sublayer boundary.  XS [ns][R][width] are the copies of the stream (src_ns of them valid on entry: 1 right after
 // the embedding, which is broadcast).  With hc_prev = [in | out | mix] of the sublayer that has just produced Y (+ Y2):
 //     x_t <- sum_s mix[s][t] x_s + out[t] * (Y + Y2)            for all t at once, from the old copies
+// (grouped experts: Y = null and the row's share is the sum of rows pair_dst[r * top + k] of Yg, in order of k)
 // then, with in_next: u = sum_s in_next[s] x_s of the NEW copies, norm(u) -> the next product's operand; xsum (optional) receives the
 // sum of the new copies (what follows the last layer, and what a capture keeps).  One CTA per row.
 template <typename OT>
 __global__ void __launch_bounds__(256) k_hc_step(float* __restrict__ XS, size_t stream_stride, int ns, int src_ns, int width,
-                                                 const float* __restrict__ Y, const float* __restrict__ Y2, const float* __restrict__ hc_prev,
+                                                 const float* __restrict__ Y, const float* __restrict__ Y2, const float* __restrict__ Yg,
+                                                 const int* __restrict__ pair_dst, int top, const float* __restrict__ hc_prev,
                                                  const float* __restrict__ in_next, NormArgs nrm, OT* __restrict__ op, int ld_op,
                                                  float* __restrict__ xsum) {
     __shared__ float red[33];
     __shared__ float sh[2 * HC_MAX + HC_MAX * HC_MAX + HC_MAX];
+    __shared__ int sdst[PN_MAX_TOP];
     const int r = blockIdx.x;
+    if (Yg && threadIdx.x < top) sdst[threadIdx.x] = pair_dst[(size_t)r * top + threadIdx.x];
     float* s_out = sh + HC_MAX;               // (sh: in of the previous sublayer, unused) | out | mix | in_next
     float* s_mix = sh + 2 * HC_MAX;
     float* s_in = sh + 2 * HC_MAX + HC_MAX * HC_MAX;
@@ -58,7 +62,9 @@ __global__ void __launch_bounds__(256) k_hc_step(float* __restrict__ XS, size_t 
         for (int s = 0; s < HC_MAX; s++)
             if (s < ns) xo[s] = XS[(size_t)(s < src_ns ? s : 0) * stream_stride + (size_t)r * width + c];
         if (hc_prev) {
-            float y = Y[(size_t)r * width + c];
+            float y = 0.0f;
+            if (Yg) { for (int k = 0; k < top; k++) y += Yg[(size_t)sdst[k] * width + c]; }
+            else y = Y[(size_t)r * width + c];
             if (Y2) y += Y2[(size_t)r * width + c];
 #pragma unroll
             for (int t = 0; t < HC_MAX; t++)
@@ -162,6 +168,50 @@ __global__ void __launch_bounds__(128) k_lat_prep(PassTables t, LatAttn b, const
         sc = 1.0f / sqrtf(ss / (float)b.q_rank + b.eps);
         for (int i = threadIdx.x; i < ld_q; i += blockDim.x) opq[(size_t)r * ld_q + i] = cvt<OT>(i < b.q_rank ? p[b.q_off + i] * sc * b.q_norm[i] : 0.0f);
     }
+}
+
+// Prompt portions: the heads' queries with their rotated part turned to the row's position, and the heads' gate logits behind them:
+// QR [R][ld_qr] = [heads x (plain | rotated) | heads gates].  Q may be QR itself (in place).
+__global__ void __launch_bounds__(128) k_lat_qrot(PassTables t, LatAttn b, const float* __restrict__ Q, int ldq, int q0, const float* __restrict__ P, int ldp,
+                                                  float* __restrict__ QR, int ld_qr) {
+    const int r = blockIdx.x, hd = b.dim + b.rope;
+    const float fpos = (float)t.row_pos[r];
+    const float* q = Q + (size_t)r * ldq + q0;
+    float* o = QR + (size_t)r * ld_qr;
+    const int half = b.rot_dims / 2;
+    for (int e = threadIdx.x; e < b.heads * hd; e += blockDim.x) {
+        const int h = e / hd, i = e % hd, j = i - b.dim;
+        if (j < 0 || j >= b.rot_dims) { if (o + e != q + e) o[e] = q[e]; continue; }
+        const int pr = b.rot_layout ? j >> 1 : (j < half ? j : j - half);
+        const bool first = b.rot_layout ? (j & 1) == 0 : j < half;
+        if (!first) continue;                     // the pair's first entry writes both
+        int i0, i1;
+        rot_pair(b, pr, i0, i1);
+        float sn, cs;
+        sincosf(fpos * b.inv_freq[pr], &sn, &cs);
+        const float u = q[h * hd + b.dim + i0], v = q[h * hd + b.dim + i1];
+        o[h * hd + b.dim + i0] = u * cs - v * sn;
+        o[h * hd + b.dim + i1] = v * cs + u * sn;
+    }
+    if (P) for (int h = threadIdx.x; h < b.heads; h += blockDim.x) o[b.heads * hd + h] = P[(size_t)r * ldp + b.g_off + h];
+}
+
+// Expanded keys and values of n cached tokens of one slot from position lo: X [n][heads * (dim + vdim)] (fp32) holds [uk c | uv c];
+// Kx [n_slots][max_ctx][heads][dim + rope] <- [plain key | the cached rotated part], Vx [n_slots][max_ctx][heads][vdim].
+__global__ void __launch_bounds__(256) k_lat_pack(LatAttn b, const float* __restrict__ X, int n, int slot, int lo, const bf16* __restrict__ cache,
+                                                  bf16* __restrict__ Kx, bf16* __restrict__ Vx) {
+    const int j = blockIdx.x, hd = b.dim + b.rope;
+    const size_t row = (size_t)slot * b.max_ctx + lo + j;
+    const float* x = X + (size_t)j * b.heads * (b.dim + b.vdim);
+    const bf16* cr = cache + row * b.c_ld + b.rank;
+    bf16* k = Kx + row * (size_t)(b.heads * hd);
+    bf16* v = Vx + row * (size_t)(b.heads * b.vdim);
+    for (int e = threadIdx.x; e < b.heads * hd; e += blockDim.x) {
+        const int h = e / hd, i = e % hd;
+        k[e] = i < b.dim ? __float2bfloat16_rn(x[h * b.dim + i]) : cr[i - b.dim];
+    }
+    const float* xv = x + b.heads * b.dim;
+    for (int e = threadIdx.x; e < b.heads * b.vdim; e += blockDim.x) v[e] = __float2bfloat16_rn(xv[e]);
 }
 
 // Absorbed query of (row, head): qa[0 .. rank) = sum_d q_plain[d] uk[head * dim + d][:], qa[rank ..) = the rotated part at the row's

@@ -191,12 +191,12 @@ __global__ void __launch_bounds__(128) k_sattn_mma(PassTables t, SoftAttn b, int
             if (c + x >= b.vdim) continue;
             if (r_lo < nq) {
                 float v = o[n][x] * i_lo;
-                if (b.gate) { const float gt = P[(size_t)(row0 + r_lo) * ldp + b.g_off + h * b.vdim + c + x]; v *= b.gate == 2 ? sigmoidf_(gt) : gt * sigmoidf_(gt); }
+                if (b.gate) { const float gt = P[(size_t)(row0 + r_lo) * ldp + b.g_off + (b.gate == 3 ? h : h * b.vdim + c + x)]; v *= b.gate >= 2 ? sigmoidf_(gt) : gt * sigmoidf_(gt); }
                 out[(size_t)(row0 + r_lo) * ld_out + b.a_off + h * b.vdim + c + x] = __float2bfloat16_rn(v);
             }
             if (r_hi < nq) {
                 float v = o[n][2 + x] * i_hi;
-                if (b.gate) { const float gt = P[(size_t)(row0 + r_hi) * ldp + b.g_off + h * b.vdim + c + x]; v *= b.gate == 2 ? sigmoidf_(gt) : gt * sigmoidf_(gt); }
+                if (b.gate) { const float gt = P[(size_t)(row0 + r_hi) * ldp + b.g_off + (b.gate == 3 ? h : h * b.vdim + c + x)]; v *= b.gate >= 2 ? sigmoidf_(gt) : gt * sigmoidf_(gt); }
                 out[(size_t)(row0 + r_hi) * ld_out + b.a_off + h * b.vdim + c + x] = __float2bfloat16_rn(v);
             }
         }

@@ -112,7 +112,7 @@ def synth_tensors(desc: dict, seed: int = 0, gain: float = 1.0) -> dict:
     rng = np.random.default_rng(seed)
     S, out = desc["streams"], {}
     for name, shape in tensor_shapes(desc).items():
-        parts = name.split(".")
+        parts = ("." + name).split(".")
         leaf = parts[-1]
         if leaf == "alpha":
             a = np.asarray(0.5 + 0.2 * rng.random())

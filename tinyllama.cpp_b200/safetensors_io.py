@@ -31,7 +31,7 @@ def read(path) -> dict:
 def f32_to_bf16_bits(a: np.ndarray) -> np.ndarray:
     """Round-to-nearest-even bfloat16 bit patterns of a float32 array."""
     u = np.ascontiguousarray(a, np.float32).view(np.uint32).astype(np.uint64)
-    return ((u + 0x7FFF + ((u >> 16) & 1)) >> 16).astype(np.uint16)
+    return ((u + 0x7FFF + ((u >> 16) & 1)) >> 16).astype(np.uint16).reshape(np.shape(a))
 
 
 def bf16_bits_to_f32(b: np.ndarray) -> np.ndarray:
@@ -43,7 +43,7 @@ def write(path, tensors: dict) -> None:
     header, off, blobs = {}, 0, []
     for name, (dt, arr) in tensors.items():
         b = np.ascontiguousarray(arr).tobytes()
-        header[name] = {"dtype": dt, "shape": list(arr.shape), "data_offsets": [off, off + len(b)]}
+        header[name] = {"dtype": dt, "shape": list(np.shape(arr)), "data_offsets": [off, off + len(b)]}       # () stays (): a scalar tensor
         off += len(b)
         blobs.append(b)
     h = json.dumps(header, separators=(",", ":")).encode()
