@@ -160,7 +160,8 @@ int gtb_seq_last_logits(gtb_seq_t m, int seg, float* h_logits);
  * "tensor" (1, default: bf16 matrix products of >= "tensor_min_rows" rows on tcgen05; 0: SIMT kernels only),
  * "tensor_min_rows" (default 64), "graph" (1, default: gtb_seq_decode replays a CUDA graph per step),
  * "fused_attn" (1, default: tiled kernels of the mixers on prompt portions -- tensor-core attention in bf16 mode, chunked
- * retention and minGRU; 0: the row-at-a-time kernels), "grouped_experts" (1, default: rows sorted by expert and multiplied as groups
+ * retention and minGRU, expanded keys and values for latent attention; decode rows of latent attention on tensor cores in bf16 mode;
+ * 0: the row-at-a-time kernels), "grouped_experts" (1, default: rows sorted by expert and multiplied as groups
  * on passes of tensor_min_rows rows or more; 0: one weight stream per row and choice), "fused_norm" (1, default: norm and input convolution in one kernel on passes of 32 rows or more; 0: two kernels) */
 int gtb_seq_set_option(gtb_seq_t m, const char* name, int value);
 int gtb_seq_read_capture(gtb_seq_t m, int run, int row, float* h_out);    /* [width] */

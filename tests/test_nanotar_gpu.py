@@ -414,6 +414,32 @@ def test_tiled_kernels_on_portions(lib, mode, layers):
     assert rel(nxt, R.forward(cfg, W, np.append(a, 5))[-1:]) < (TOL[mode] if mode == "float32" else 2.0)
 
 
+@pytest.mark.parametrize("layers", [
+    [L(heads=3, dim=10, rot_dim=6, vdim=14, kv_rank=27), L(heads=20, dim=8, rot_dim=8, vdim=8, kv_rank=40, q_rank=16, window=70)],      # latents that are multiples of nothing, two groups of heads
+    [L(heads=16, dim=16, rot_dim=16, vdim=16, kv_rank=144, q_rank=24, window=33, mlp=D(32)), L(heads=2, dim=16, rot_dim=8, vdim=16, kv_rank=264)],
+])
+def test_decode_rows_on_tensor_cores(lib, layers):
+    """bfloat16 decode rows take the heads of a row as the M dimension of one tensor-core tile over the cached latents: three sequences at
+    unequal positions (inside the first key tile, across several, past a window) decoded together -- against the restatement and against
+    the row kernels (option fused_attn = 0)."""
+    cfg = NT.make_config(vocab=64, width=64, layers=layers)
+    m, W = make(lib, cfg, "bfloat16", seed=63, n_slots=6, max_ctx=400)
+    seqs = [toks(140 + i, n, 64) for i, n in enumerate((9, 150, 331))]
+    want = [R.forward(cfg, W, q) for q in seqs]
+    outs = {}
+    for fused in (1, 0):
+        m.set_option("fused_attn", fused)
+        base = 0 if fused else 3
+        for i, q in enumerate(seqs):
+            m.step([(base + i, q[:-4])])
+        rows = [m.step([(base + i, q[len(q) - 4 + k:len(q) - 3 + k]) for i, q in enumerate(seqs)], range(3)) for k in range(4)]
+        got = np.stack(rows, 1)                          # [sequence, step, vocab]
+        for i in range(3):
+            assert rel(got[i], want[i][-4:]) < TOL["bfloat16"], (fused, i)
+        outs[fused] = got
+    assert rel(outs[1].reshape(12, -1), outs[0].reshape(12, -1)) < TOL["bfloat16"]
+
+
 def test_tensor_core_path_with_awkward_sizes(lib):
     """bfloat16 mode, portions of 64 rows and more: the tcgen05 products (fused gate-times-up epilogues, grouped experts) and the
     tiled attention with sizes that are multiples of nothing, against the SIMT kernels."""

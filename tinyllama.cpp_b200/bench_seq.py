@@ -1,6 +1,8 @@
 """`bench.py --workload reninex`: prefill and decode throughput of the Reninex family at layer sizes that resemble a real model
 (random weights), beside TinyLlama at the same layer shape and layer count.  `bench.py --workload robopel`: the same for the Robopel
-family, beside Reninex (the closest existing model: same library, same width and layer count).  Timed with CUDA events on each library's own stream,
+family, beside Reninex (the closest existing model: same library, same width and layer count).  `bench.py --workload nanotar`: the Nanotar
+family beside Robopel (the closest existing model: softmax attention with a window, a sink and an output gate, routed experts) at the same
+widths and layer count.  Timed with CUDA events on each library's own stream,
 after warm-up; the weights of one pass (hundreds of MB) are larger than L2, so every pass streams them from HBM."""
 from __future__ import annotations
 
@@ -232,6 +234,148 @@ def robopel_section(torch, name, T, iters, warmup, peaks):
     out["state_bytes_per_slot_at_T"] = state_bytes
     m.close()
     return out
+
+
+NANOTAR_SIZES = {
+    # width, dense ff, heads x (plain + rotated | value), latent ranks, window of the second form, experts x ff (top) + shared ff, stream copies
+    "w2048": dict(width=2048, ff=5632, heads=16, dim=96, rot=32, vdim=128, kv_rank=512, q_rank=768, window=1024, experts=16, top=2, eff=1408, sff=1408, streams=2),
+    "w1024": dict(width=1024, ff=2816, heads=8, dim=96, rot=32, vdim=128, kv_rank=256, q_rank=384, window=512, experts=16, top=2, eff=704, sff=704, streams=2),
+}
+
+
+def nanotar_config(name, vocab=32000):
+    """Four layers: causal latent attention + dense, windowed form (query latent, sink) + experts, causal + experts, windowed + dense."""
+    from . import nanotar as NT
+    z = NANOTAR_SIZES[name]
+    att = dict(heads=z["heads"], dim=z["dim"], rot_dim=z["rot"], vdim=z["vdim"], kv_rank=z["kv_rank"], rot_base=500000.0)
+    moe = lambda: NT.moe_mlp(experts=z["experts"], top=z["top"], ff=z["eff"], shared_ff=z["sff"])
+    layers = [NT.latent_layer(mlp=NT.dense_mlp(z["ff"]), **att), NT.latent_layer(q_rank=z["q_rank"], window=z["window"], mlp=moe(), **att),
+              NT.latent_layer(mlp=moe(), **att), NT.latent_layer(q_rank=z["q_rank"], window=z["window"], mlp=NT.dense_mlp(z["ff"]), **att)]
+    return NT.make_config(vocab=vocab, width=z["width"], streams=z["streams"], layers=layers, eps=1e-6, logit_softcap=30.0)
+
+
+def nanotar_counts(desc, T):
+    """(weights every token multiplies, FLOPs of the attention's own arithmetic for a T-token prompt, bytes of weights a decode step of one
+    sequence reads) -- routed experts count `top` experts per token; keys and values count one up-projection per token."""
+    from .seq import FF_GATED_EXPERTS
+    W, params, mix = desc["width"], 0, 0.0
+    for l in desc["layers"]:
+        b = l["branches"][0]
+        H, hd = b["heads"], b["dim"] + b["rope_dim"]
+        per = W * ((b["q_rank"] or H * hd) + b["kv_rank"] + b["rope_dim"] + H) + b["q_rank"] * H * hd + b["kv_rank"] * H * (b["dim"] + b["vdim"]) + W * H * b["vdim"]
+        win = b.get("window", 0)
+        keys = sum(min(i + 1, win) for i in range(T)) if win else T * (T + 1) / 2
+        mix += 2.0 * H * (hd + b["vdim"]) * keys
+        if l["ff"]:
+            per += (W * (l["experts"] + 1) + l["top"] * 3 * W * l["ff"] + 3 * W * l.get("shared_ff", 0)) if l.get("ff_kind") == FF_GATED_EXPERTS else 3 * W * l["ff"]
+        params += per
+    return params + desc["vocab"] * W, mix, 2 * (params + desc["vocab"] * W)
+
+
+def nanotar_section(torch, name, T, iters, warmup, peaks):
+    from . import nanotar as NT, seq
+    cfg = nanotar_config(name)
+    desc = NT.describe(cfg)
+    t0 = time.time()
+    rng = np.random.default_rng(0)
+    S, tensors = desc["streams"], {}
+    for k, shape in NT.tensor_shapes(desc).items():              # cheap random bf16 patterns of the right scale
+        n = int(np.prod(shape)) if shape else 1
+        parts = ("." + k).split(".")
+        leaf = parts[-1]
+        if leaf == "alpha":
+            a = NT.st.f32_to_bf16_bits(np.full(n, 0.5, np.float32))
+        elif leaf == "b" and "norm" in parts[-2]:
+            a = np.zeros(n, np.uint16)
+        elif leaf in ("norm1", "norm2", "norm"):
+            a = np.full(n, 0x3F80, np.uint16)
+        elif parts[-2].startswith("hc"):
+            a = NT.st.f32_to_bf16_bits({"in": np.full(shape, 1.0 / S), "out": np.ones(shape), "mix": np.eye(S)}[leaf].astype(np.float32).reshape(-1))
+        else:
+            std = 1.0 if k == "embed" or leaf == "sink" else 1.0 / np.sqrt(shape[-1])
+            a = NT.st.f32_to_bf16_bits(rng.standard_normal(n, np.float32) * np.float32(std))
+        tensors[k] = a.reshape(shape)
+    n_slots = 8
+    m = seq.SeqModel(desc, seq.BF16, n_slots, T + 64, max_rows=T).load(tensors)
+    stream = torch.cuda.ExternalStream(seq.stream_handle(), device=torch.device("cuda", 0))
+    prompt = rng.integers(0, desc["vocab"], T).astype(np.int32)
+    params, mix, dec_bytes = nanotar_counts(desc, T)
+    out = {"size": name, "layers": len(desc["layers"]), "params_matmul_per_token": params, "weight_bytes": m.weight_bytes(), "setup_s": round(time.time() - t0, 1)}
+
+    def prefill():
+        m.reset(0)
+        m.step([(0, prompt)], [T - 1])
+    l0 = seq.launch_count()
+    prefill()
+    out["prefill_launches"] = seq.launch_count() - l0
+    ms = _events(torch, stream, prefill, iters, warmup)
+    flops = 2.0 * T * params - 2.0 * (T - 1) * desc["vocab"] * desc["width"] + mix
+    out["prefill"] = {"T": T, "ms": ms, "tokens_per_s": T / ms * 1e3, "tflops": flops / ms * 1e-9, "frac_of_bf16_peak": flops / ms * 1e-9 / peaks["tflops"],
+                      "note": "includes the host->device copy of the prompt and the device->host copy of the last row's logits; experts count top per token"}
+
+    def chunked():                                                # the same prompt in four portions: every portion expands the latents before it again
+        m.reset(0)
+        for i in range(0, T, T // 4):
+            m.step([(0, prompt[i:i + T // 4])], [T // 4 - 1])
+    out["prefill_in_4_portions_ms"] = _events(torch, stream, chunked, max(3, iters // 2), 2)
+    for s in range(n_slots):
+        m.reset(s)
+        m.step_greedy([(s, prompt[: T - 40])])
+    state_bytes = m.state_bytes_per_slot() * (T - 40) / (T + 64)
+    for nseq in (1, 8):
+        slots, steps = list(range(nseq)), 8
+        m.decode(slots, 2)
+        t_ms = []
+        with torch.cuda.stream(stream):
+            for _ in range(3):
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record(stream)
+                m.decode(slots, steps)
+                b.record(stream)
+                torch.cuda.synchronize()
+                t_ms.append(a.elapsed_time(b) / steps)
+        ms = float(np.median(t_ms))
+        by = dec_bytes
+        out[f"decode_{nseq}"] = {"ms_per_step": ms, "tokens_per_s": nseq / ms * 1e3, "bytes_per_step_one_sequence": by, "gbs": by / ms * 1e-6,
+                                 "frac_of_hbm_peak": by / ms * 1e-6 / peaks["hbm_gbs"],
+                                 "note": "bytes: weights one sequence's step reads (top experts per routed layer); further sequences add their experts and cached latents"}
+    out["state_bytes_per_slot_at_T"] = state_bytes
+    m.close()
+    return out
+
+
+def _peaks(root):
+    p = root / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return {"hbm_gbs": float(d["hbm_gbs"]), "tflops": float(d.get("bf16_tflops", 1590.0)), "source": "measured (MEASURED_PEAKS.json)"}
+    return {"hbm_gbs": 6650.0, "tflops": 1590.0, "source": "fallback"}
+
+
+def run_nanotar(args, root, clock_sampler) -> None:
+    """`--workload nanotar`: Nanotar at two sizes, Robopel at the same widths and layer count in the same call."""
+    import torch
+    from . import build, seq
+    build.build(target="seq")
+    torch.cuda.set_device(0)
+    peaks = _peaks(root)
+    seq.init(0)
+    T = 2048
+    iters = max(3, min(args.steps if args.steps != 512 else 5, 20))
+    warm = max(args.warmup if args.warmup != 16 else 3, 3)
+    res = {"nanotar": [], "robopel_same_width": [], "peaks": peaks}
+    with clock_sampler(0) as clk:
+        for name in NANOTAR_SIZES:
+            res["nanotar"].append(nanotar_section(torch, name, T, iters, warm, peaks))
+        for name in ROBOPEL_SIZES:
+            res["robopel_same_width"].append(robopel_section(torch, name, T, iters, warm, peaks))
+    head = res["nanotar"][0]
+    print(json.dumps({"metric": "nanotar_prefill_tokens_per_s", "value": head["prefill"]["tokens_per_s"], "unit": "tokens/s", "n_gpus": 1,
+                      "steps": iters, "warmup": warm, "ms_per_step": head["prefill"]["ms"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+                      "dtype": "bf16 operands, fp32 accumulation; fp32 stream copies, norms, scores, router", "data": "synthetic",
+                      "config": {"workload": f"Nanotar {head['size']} x {head['layers']} layers, random weights: prefill of {T} tokens; decode at that context",
+                                 "l2": "weights of a pass exceed L2"},
+                      "detail": res, "gpu_launches": head["prefill_launches"], "clocks": clk.summary()}), flush=True)
 
 
 def tinyllama_section(torch, layers, T, iters, warmup, peaks):

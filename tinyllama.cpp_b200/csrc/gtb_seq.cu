@@ -460,7 +460,14 @@ NormArgs norm_args(const gtb_seq_model* m, const LayerW& l, int q) {
 template <typename OT>
 int hc_boundary(gtb_seq_model* m, int R, PendingUpdate& pend, const float* hc_next, const NormArgs& nrm, float* xsum) {
     const int W = m->cfg.width;
-    k_hc_step<OT><<<R, 256, 0, ctx().stream>>>(m->xs, (size_t)m->max_rows * W, m->ns, pend.src_ns, W, pend.Y, pend.Y2, pend.Yg, pend.pair_dst, pend.top, pend.hc, hc_next, nrm, (OT*)m->opA, m->wp, xsum);
+    const bool whole_row = hc_next && nrm.kind == GTB_NORM_RMS;       // the RMS norm sums over the row inside one CTA
+    const int V = W % 4 == 0 ? 4 : 1;
+    const int gy = whole_row ? 1 : std::max(1, std::min((W / V + 255) / 256, std::max(1, 2048 / R)));
+#define HC_LAUNCH(VV, NN) k_hc_step<OT, VV, NN><<<dim3(R, gy), 256, 0, ctx().stream>>>(m->xs, (size_t)m->max_rows * W, m->ns, pend.src_ns, W, pend.Y, pend.Y2, pend.Yg, \
+                                                                                      pend.pair_dst, pend.top, pend.hc, hc_next, nrm, (OT*)m->opA, m->wp, xsum)
+    if (V == 4) { if (m->ns <= 2) HC_LAUNCH(4, 2); else if (m->ns <= 4) HC_LAUNCH(4, 4); else HC_LAUNCH(4, 8); }
+    else { if (m->ns <= 2) HC_LAUNCH(1, 2); else if (m->ns <= 4) HC_LAUNCH(1, 4); else HC_LAUNCH(1, 8); }
+#undef HC_LAUNCH
     GTB_LAUNCHED();
     pend = PendingUpdate{};
     pend.src_ns = m->ns;
@@ -481,6 +488,25 @@ SoftAttn lat_soft_args(const gtb_seq_model* m, const BranchW& b) {
     a.scale = b.d.scale; a.eps = m->cfg.eps; a.window = b.d.window; a.sink = b.d_sink;
     a.k_ld = a.v_ld = b.c_ld; a.own_kv = 1; a.max_ctx = m->cfg.max_ctx;
     return a;
+}
+
+template <int VPW>
+int launch_lat_dec_mma(const PassTables& t, const SoftAttn& a, int R, int splits, const float* QA, int ldqa, const bf16* cache, float* part) {
+    const int DP = (a.dim + 15) & ~15;
+    const size_t smem = (size_t)(16 + 64) * (DP + 8) * 2 + 16 * (64 + 8) * 2 + 64 * sizeof(float);
+    static size_t allowed = 48 * 1024;
+    if (smem > 200 * 1024) return -1;
+    if (smem > allowed) { GTB_CUDA(cudaFuncSetAttribute(k_lat_dec_mma<VPW>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); allowed = smem; }
+    k_lat_dec_mma<VPW><<<dim3(R, (a.heads + 15) / 16, splits), 128, smem, ctx().stream>>>(t, a, QA, ldqa, cache, part, R);
+    GTB_LAUNCHED();
+    return GTB_OK;
+}
+// -1: sizes outside the kernel (the caller takes the row kernels)
+int lat_dec_mma(const PassTables& t, const SoftAttn& a, int R, int splits, const float* QA, int ldqa, const bf16* cache, float* part) {
+    if (a.vdim <= 128) return launch_lat_dec_mma<32>(t, a, R, splits, QA, ldqa, cache, part);
+    if (a.vdim <= 256) return launch_lat_dec_mma<64>(t, a, R, splits, QA, ldqa, cache, part);
+    if (a.vdim <= 512) return launch_lat_dec_mma<128>(t, a, R, splits, QA, ldqa, cache, part);
+    return -1;
 }
 
 // One pre-norm layer on R rows.  pend carries the update of the sublayer before it (none for the first layer) and leaves with this
@@ -539,13 +565,25 @@ int run_prenorm_layer(gtb_seq_model* m, const PassTables& t, int R, int S, const
         const int hd = a.dim + a.rope;
         const float* Q = a.q_rank > 0 ? m->latQ : m->P;
         const int ldq = a.q_rank > 0 ? a.heads * hd + a.heads : l.n1, q0 = a.q_rank > 0 ? 0 : b.q_off;
-        k_lat_qabs<<<dim3(R, a.heads), 128, hd * sizeof(float), st>>>(t, a, Q, ldq, q0, b.w_uk, b.rank_p, m->latQA);
+        k_lat_qabs<<<dim3(R, a.heads, (a.rank + 127) / 128), 128, (hd + 512) * sizeof(float), st>>>(t, a, Q, ldq, q0, b.w_uk, b.rank_p, m->latQA);
         GTB_LAUNCHED();
         const SoftAttn sa = lat_soft_args(m, b);
         const int ldqa = a.heads * sa.dim, ld_ol = (a.heads * a.rank + 7) / 8 * 8;
         const size_t smem = (sa.dim + 128 + 33) * sizeof(float);
         bool done = false;
-        if (!portions && R <= SPLIT_MAX_ROWS && m->sattn_part) {
+        if (sizeof(OT) == 2 && m->fused_attn && !portions && R <= SPLIT_MAX_ROWS && m->sattn_part) {
+            // decode rows in bf16 mode: 16 heads per CTA on tensor cores, one CTA per 64 keys of the longest key list this layer can meet
+            const int max_keys = sa.window > 0 ? std::min(c.max_ctx, sa.window) : c.max_ctx;
+            const int splits = std::max(1, std::min(32, (max_keys + 63) / 64));
+            rc = lat_dec_mma(t, sa, R, splits, m->latQA, ldqa, (const bf16*)run.kc[0], m->sattn_part);
+            if (rc > 0) return rc;
+            if (rc == 0) {
+                k_sattn_join<OT><<<dim3(R, sa.heads), 128, 0, st>>>(sa, m->latQA, ldqa, m->sattn_part, R, splits, (OT*)m->opO, ld_ol);
+                GTB_LAUNCHED();
+                done = true;
+            }
+        }
+        if (!done && !portions && R <= SPLIT_MAX_ROWS && m->sattn_part) {
             const int max_keys = sa.window > 0 ? std::min(c.max_ctx, sa.window) : c.max_ctx;
             const int splits = std::max(1, std::min(32, (max_keys + 127) / 128));
             if (splits > 1) {

@@ -31,8 +31,22 @@ __device__ __forceinline__ float silu_(float z) { return z * sigmoidf_(z); }
 // (grouped experts: Y = null and the row's share is the sum of rows pair_dst[r * top + k] of Yg, in order of k)
 // then, with in_next: u = sum_s in_next[s] x_s of the NEW copies, norm(u) -> the next product's operand; xsum (optional) receives the
 // sum of the new copies (what follows the last layer, and what a capture keeps).  One CTA per row.
-template <typename OT>
-__global__ void __launch_bounds__(256) k_hc_step(float* __restrict__ XS, size_t stream_stride, int ns, int src_ns, int width,
+template <int V> struct HcVec { float v[V]; };
+template <int V> __device__ __forceinline__ HcVec<V> hc_load(const float* p) {
+    HcVec<V> o;
+    if (V == 4) { const float4 t = *reinterpret_cast<const float4*>(p); o.v[0] = t.x; o.v[1] = t.y; o.v[2] = t.z; o.v[3] = t.w; }
+    else o.v[0] = *p;
+    return o;
+}
+template <int V> __device__ __forceinline__ void hc_store(float* p, const HcVec<V>& a) {
+    if (V == 4) *reinterpret_cast<float4*>(p) = make_float4(a.v[0], a.v[1], a.v[2], a.v[3]);
+    else *p = a.v[0];
+}
+// V = 4: width, ld_op and every base are multiples of four elements (16-byte accesses); V = 1 otherwise.  NSM: the most copies this
+// instance takes (its register arrays are that long).  grid (rows, column groups); an RMS norm needs the whole row in one CTA
+// (gridDim.y = 1).
+template <typename OT, int V, int NSM>
+__global__ void __launch_bounds__(256, NSM <= 4 ? 3 : 2) k_hc_step(float* __restrict__ XS, size_t stream_stride, int ns, int src_ns, int width,
                                                  const float* __restrict__ Y, const float* __restrict__ Y2, const float* __restrict__ Yg,
                                                  const int* __restrict__ pair_dst, int top, const float* __restrict__ hc_prev,
                                                  const float* __restrict__ in_next, NormArgs nrm, OT* __restrict__ op, int ld_op,
@@ -54,43 +68,64 @@ __global__ void __launch_bounds__(256) k_hc_step(float* __restrict__ XS, size_t 
     }
     __syncthreads();
     const bool rms = in_next && nrm.kind == 0;
+    const float alpha = (in_next && !rms) ? nrm.alpha[0] : 0.0f;
     float ss = 0.0f;
     // pass 1 rewrites the copies (and gathers the mean square of u for an RMS norm); pass 2 (RMS only) re-reads them
-    for (int c = threadIdx.x; c < width; c += blockDim.x) {
-        float xo[HC_MAX], xn[HC_MAX];
+    for (int c = (blockIdx.y * blockDim.x + threadIdx.x) * V; c < width; c += gridDim.y * blockDim.x * V) {
+        const size_t at = (size_t)r * width + c;
+        HcVec<V> xo[NSM], y, u, sum;
 #pragma unroll
-        for (int s = 0; s < HC_MAX; s++)
-            if (s < ns) xo[s] = XS[(size_t)(s < src_ns ? s : 0) * stream_stride + (size_t)r * width + c];
+        for (int s = 0; s < NSM; s++)
+            if (s < ns) xo[s] = hc_load<V>(XS + (size_t)(s < src_ns ? s : 0) * stream_stride + at);
+#pragma unroll
+        for (int i = 0; i < V; i++) y.v[i] = u.v[i] = sum.v[i] = 0.0f;
         if (hc_prev) {
-            float y = 0.0f;
-            if (Yg) { for (int k = 0; k < top; k++) y += Yg[(size_t)sdst[k] * width + c]; }
-            else y = Y[(size_t)r * width + c];
-            if (Y2) y += Y2[(size_t)r * width + c];
+            if (Yg) {
+                for (int k = 0; k < top; k++) {
+                    const HcVec<V> g = hc_load<V>(Yg + (size_t)sdst[k] * width + c);
 #pragma unroll
-            for (int t = 0; t < HC_MAX; t++)
-                if (t < ns) {
-                    float a = s_out[t] * y;
-#pragma unroll
-                    for (int s = 0; s < HC_MAX; s++)
-                        if (s < ns) a = fmaf(s_mix[s * ns + t], xo[s], a);
-                    xn[t] = a;
+                    for (int i = 0; i < V; i++) y.v[i] += g.v[i];
                 }
-        } else {
+            } else y = hc_load<V>(Y + at);
+            if (Y2) {
+                const HcVec<V> g = hc_load<V>(Y2 + at);
 #pragma unroll
-            for (int t = 0; t < HC_MAX; t++) if (t < ns) xn[t] = xo[t];
-        }
-        float u = 0.0f, sum = 0.0f;
-#pragma unroll
-        for (int t = 0; t < HC_MAX; t++)
-            if (t < ns) {
-                if (hc_prev || t >= src_ns) XS[(size_t)t * stream_stride + (size_t)r * width + c] = xn[t];
-                sum += xn[t];
-                if (in_next) u = fmaf(s_in[t], xn[t], u);
+                for (int i = 0; i < V; i++) y.v[i] += g.v[i];
             }
-        if (xsum) xsum[(size_t)r * width + c] = sum;
+        }
+#pragma unroll
+        for (int t = 0; t < NSM; t++)
+            if (t < ns) {
+                HcVec<V> xt = xo[t];
+                if (hc_prev) {
+#pragma unroll
+                    for (int i = 0; i < V; i++) {
+                        float a = s_out[t] * y.v[i];
+#pragma unroll
+                        for (int s = 0; s < NSM; s++)
+                            if (s < ns) a = fmaf(s_mix[s * ns + t], xo[s].v[i], a);
+                        xt.v[i] = a;
+                    }
+                }
+                if (hc_prev || t >= src_ns) hc_store<V>(XS + (size_t)t * stream_stride + at, xt);
+#pragma unroll
+                for (int i = 0; i < V; i++) {
+                    sum.v[i] += xt.v[i];
+                    if (in_next) u.v[i] = fmaf(s_in[t], xt.v[i], u.v[i]);
+                }
+            }
+        if (xsum) hc_store<V>(xsum + at, sum);
         if (in_next) {
-            if (rms) ss += u * u;
-            else op[(size_t)r * ld_op + c] = cvt<OT>(fmaf(tanhf(nrm.alpha[0] * u), nrm.w[c], nrm.b[c]));
+            if (rms) {
+#pragma unroll
+                for (int i = 0; i < V; i++) ss += u.v[i] * u.v[i];
+            } else {
+                float o[V];
+#pragma unroll
+                for (int i = 0; i < V; i++) o[i] = fmaf(tanhf(alpha * u.v[i]), nrm.w[c + i], nrm.b[c + i]);
+                if (V == 4) store4(op + (size_t)r * ld_op + c, o[0], o[1], o[2], o[3]);
+                else op[(size_t)r * ld_op + c] = cvt<OT>(o[0]);
+            }
         }
     }
     if (!rms) return;
@@ -215,26 +250,42 @@ __global__ void __launch_bounds__(256) k_lat_pack(LatAttn b, const float* __rest
 }
 
 // Absorbed query of (row, head): qa[0 .. rank) = sum_d q_plain[d] uk[head * dim + d][:], qa[rank ..) = the rotated part at the row's
-// position.  Q [R][ldq] holds the heads' [plain | rotated] queries from column q0; QA [R][heads * (rank + rope)].  uk [heads * dim][ld_uk].
+// position.  Q [R][ldq] holds the heads' [plain | rotated] queries from column q0; QA [R][heads * (rank + rope)].  uk [heads * dim][ld_uk],
+// ld_uk a multiple of 64 with zero columns beyond rank.  grid (rows, heads, groups of 128 latent columns); the CTA's four warps split
+// the plain entries, a lane takes four adjacent columns (one 8-byte load per entry), the warps' sums meet in shared memory.
 __global__ void __launch_bounds__(128) k_lat_qabs(PassTables t, LatAttn b, const float* __restrict__ Q, int ldq, int q0, const bf16* __restrict__ uk, int ld_uk,
                                                   float* __restrict__ QA) {
-    extern __shared__ float sq[];             // [dim + rope]
+    extern __shared__ float sq[];             // [dim + rope], then [4][128] partial sums
     const int r = blockIdx.x, h = blockIdx.y, hd = b.dim + b.rope;
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    float* part = sq + hd;
     const float* q = Q + (size_t)r * ldq + q0 + (size_t)h * hd;
     for (int i = threadIdx.x; i < hd; i += blockDim.x) sq[i] = q[i];
     __syncthreads();
     float* qa = QA + ((size_t)r * b.heads + h) * (b.rank + b.rope);
-    const bf16* w = uk + (size_t)h * b.dim * ld_uk;
-    for (int c = threadIdx.x; c < b.rank; c += blockDim.x) {
-        float a0 = 0.0f, a1 = 0.0f;
-        int d = 0;
-        for (; d + 1 < b.dim; d += 2) {
-            a0 = fmaf(sq[d], __bfloat162float(w[(size_t)d * ld_uk + c]), a0);
-            a1 = fmaf(sq[d + 1], __bfloat162float(w[(size_t)(d + 1) * ld_uk + c]), a1);
+    const int c = blockIdx.z * 128 + lane * 4;
+    float a[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    if (c < b.rank) {
+        const bf16* w = uk + (size_t)h * b.dim * ld_uk + c;
+        const int d0 = (b.dim * warp) / 4, d1 = (b.dim * (warp + 1)) / 4;
+#pragma unroll 8
+        for (int d = d0; d < d1; d++) {
+            const uint2 wv = __ldg(reinterpret_cast<const uint2*>(w + (size_t)d * ld_uk));
+            const float qd = sq[d];
+            a[0] = fmaf(qd, __uint_as_float(wv.x << 16), a[0]);
+            a[1] = fmaf(qd, __uint_as_float(wv.x & 0xffff0000u), a[1]);
+            a[2] = fmaf(qd, __uint_as_float(wv.y << 16), a[2]);
+            a[3] = fmaf(qd, __uint_as_float(wv.y & 0xffff0000u), a[3]);
         }
-        if (d < b.dim) a0 = fmaf(sq[d], __bfloat162float(w[(size_t)d * ld_uk + c]), a0);
-        qa[c] = a0 + a1;
     }
+#pragma unroll
+    for (int i = 0; i < 4; i++) part[warp * 128 + lane * 4 + i] = a[i];
+    __syncthreads();
+    {
+        const int cc = blockIdx.z * 128 + threadIdx.x;
+        if (cc < b.rank) qa[cc] = (part[threadIdx.x] + part[128 + threadIdx.x]) + (part[256 + threadIdx.x] + part[384 + threadIdx.x]);
+    }
+    if (blockIdx.z != 0) return;
     const float fpos = (float)t.row_pos[r];
     const float* qr = sq + b.dim;
     for (int pr = threadIdx.x; pr < b.rot_dims / 2; pr += blockDim.x) {
@@ -246,6 +297,143 @@ __global__ void __launch_bounds__(128) k_lat_qabs(PassTables t, LatAttn b, const
         qa[b.rank + i1] = qr[i1] * cs + qr[i0] * sn;
     }
     for (int i = b.rot_dims + threadIdx.x; i < b.rope; i += blockDim.x) qa[b.rank + i] = qr[i];
+}
+
+// Decode rows in bf16 mode: the absorbed form on tensor cores.  All heads of a row share the cached latents, so a CTA takes 16 heads as
+// the M dimension of mma.sync m16n8k16 and sweeps its share of the row's keys (grid: rows x groups of 16 heads x key splits) in tiles
+// of 64: the tile [64][latent | rotated part] is staged once in shared memory as bf16 and serves both products -- S = Q' K^T (each of
+// the four warps scores 16 keys), softmax weights in fp32 against the running maximum (the warps' row maxima meet in shared memory),
+// O += P V with V = the tile's latent columns (each warp owns VPW value columns, P comes back from shared memory as bf16 A fragments).
+// Leaves (maximum, denominator, unnormalised sum) per head in part [split][R][heads][rank + 2], which k_sattn_join folds with the sink.
+// b: the one-K/V-head view of the branch (dim = rank + rope, vdim = rank, k_ld = the cache's row stride).
+template <int VPW>
+__global__ void __launch_bounds__(128) k_lat_dec_mma(PassTables t, SoftAttn b, const float* __restrict__ QA, int ldqa, const bf16* __restrict__ cache,
+                                                     float* __restrict__ part, int R) {
+    constexpr int TK = 64;
+    extern __shared__ __align__(16) unsigned char ld_raw[];
+    const int D = b.dim, DP = (D + 15) & ~15, LK = DP + 8, LP = TK + 8;
+    bf16* sq = reinterpret_cast<bf16*>(ld_raw);          // [16][LK]
+    bf16* sk = sq + 16 * LK;                             // [TK][LK]
+    bf16* sp = sk + TK * LK;                             // [16][LP]
+    float* smx = reinterpret_cast<float*>(sp + 16 * LP); // [4][16] row maxima of the warps' key groups, then their row sums
+    const int r = blockIdx.x, h0 = blockIdx.y * 16, pos = t.row_pos[r], slot = t.seg_slot[t.row_seg[r]];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gq = lane >> 2, tq = lane & 3;
+    const int lo = b.window > 0 ? max(0, pos - b.window + 1) : 0, total = pos - lo + 1;
+    const int per = ((total + (int)gridDim.z - 1) / (int)gridDim.z + TK - 1) / TK * TK;
+    const int n_lo = blockIdx.z * per, n_hi = min(total, n_lo + per);
+    const int nh = min(16, b.heads - h0);
+    float* out = part + (((size_t)blockIdx.z * R + r) * b.heads + h0) * (b.vdim + 2);
+    if (n_lo >= n_hi) {
+        if (threadIdx.x < nh) { out[(size_t)threadIdx.x * (b.vdim + 2)] = -INFINITY; out[(size_t)threadIdx.x * (b.vdim + 2) + 1] = 0.0f; }
+        return;
+    }
+    for (int e = threadIdx.x; e < 16 * DP; e += 128) {
+        const int hh = e / DP, i = e % DP;
+        sq[hh * LK + i] = __float2bfloat16_rn((hh < nh && i < D) ? QA[(size_t)r * ldqa + (size_t)(h0 + hh) * D + i] : 0.0f);
+    }
+    const bf16* kbase = cache + ((size_t)slot * b.max_ctx + lo) * b.k_ld;
+    const bool vec = (D % 8 == 0) && (b.k_ld % 8 == 0);
+    const uint32_t sq_a = (uint32_t)__cvta_generic_to_shared(sq), sk_a = (uint32_t)__cvta_generic_to_shared(sk), sp_a = (uint32_t)__cvta_generic_to_shared(sp);
+    float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.0f, l_hi = 0.0f;
+    float o[VPW / 8][4];
+#pragma unroll
+    for (int n = 0; n < VPW / 8; n++) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.0f; }
+    for (int j0 = n_lo; j0 < n_hi; j0 += TK) {
+        const int nk = min(TK, n_hi - j0);
+        if (vec) {
+            for (int e = threadIdx.x; e < TK * (DP / 8); e += 128) {
+                const int rr = e / (DP / 8), c8 = (e % (DP / 8)) * 8;
+                const bool ok = rr < nk && c8 < D;
+                sa_cp16(sk_a + (uint32_t)((rr * LK + c8) * 2), ok ? (const void*)(kbase + (size_t)(j0 + rr) * b.k_ld + c8) : (const void*)kbase, ok);
+            }
+            asm volatile("cp.async.commit_group;" ::: "memory");
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
+        } else {
+            for (int e = threadIdx.x; e < TK * DP; e += 128) {
+                const int rr = e / DP, i = e % DP;
+                sk[rr * LK + i] = (rr < nk && i < D) ? kbase[(size_t)(j0 + rr) * b.k_ld + i] : __float2bfloat16_rn(0.0f);
+            }
+        }
+        __syncthreads();
+        // scores of this warp's 16 keys for the 16 heads
+        float sc[2][4] = {{0.0f, 0.0f, 0.0f, 0.0f}, {0.0f, 0.0f, 0.0f, 0.0f}};
+        for (int kk = 0; kk < DP / 16; kk++) {
+            uint32_t a[4], b0, b1, b2, b3;
+            sa_ldsm_x4(sq_a + (uint32_t)((((lane & 15)) * LK + kk * 16 + (lane >> 4) * 8) * 2), a[0], a[1], a[2], a[3]);
+            sa_ldsm_x4(sk_a + (uint32_t)(((warp * 16 + (lane & 7) + (lane >> 4) * 8) * LK + kk * 16 + ((lane >> 3) & 1) * 8) * 2), b0, b1, b2, b3);
+            sa_mma(sc[0], a, b0, b1);
+            sa_mma(sc[1], a, b2, b3);
+        }
+        float mx_lo = -INFINITY, mx_hi = -INFINITY;
+#pragma unroll
+        for (int n = 0; n < 2; n++)
+#pragma unroll
+            for (int x = 0; x < 4; x++) {
+                const bool vis = warp * 16 + n * 8 + tq * 2 + (x & 1) < nk;
+                const float sv = vis ? sc[n][x] * b.scale : -INFINITY;
+                sc[n][x] = sv;
+                if (x >= 2) mx_hi = fmaxf(mx_hi, sv); else mx_lo = fmaxf(mx_lo, sv);
+            }
+        mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 1)); mx_lo = fmaxf(mx_lo, __shfl_xor_sync(0xffffffffu, mx_lo, 2));
+        mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 1)); mx_hi = fmaxf(mx_hi, __shfl_xor_sync(0xffffffffu, mx_hi, 2));
+        if (tq == 0) { smx[warp * 16 + gq] = mx_lo; smx[warp * 16 + gq + 8] = mx_hi; }
+        __syncthreads();
+        const float mn_lo = fmaxf(m_lo, fmaxf(fmaxf(smx[gq], smx[16 + gq]), fmaxf(smx[32 + gq], smx[48 + gq])));          // the tile's first key is always visible
+        const float mn_hi = fmaxf(m_hi, fmaxf(fmaxf(smx[gq + 8], smx[24 + gq]), fmaxf(smx[40 + gq], smx[56 + gq])));
+        const float c_lo = m_lo == -INFINITY ? 0.0f : __expf(m_lo - mn_lo), c_hi = m_hi == -INFINITY ? 0.0f : __expf(m_hi - mn_hi);
+        m_lo = mn_lo; m_hi = mn_hi;
+        l_lo *= c_lo; l_hi *= c_hi;
+#pragma unroll
+        for (int n = 0; n < VPW / 8; n++) { o[n][0] *= c_lo; o[n][1] *= c_lo; o[n][2] *= c_hi; o[n][3] *= c_hi; }
+#pragma unroll
+        for (int n = 0; n < 2; n++) {
+            const float w0 = sc[n][0] == -INFINITY ? 0.0f : __expf(sc[n][0] - mn_lo), w1 = sc[n][1] == -INFINITY ? 0.0f : __expf(sc[n][1] - mn_lo);
+            const float w2 = sc[n][2] == -INFINITY ? 0.0f : __expf(sc[n][2] - mn_hi), w3 = sc[n][3] == -INFINITY ? 0.0f : __expf(sc[n][3] - mn_hi);
+            l_lo += w0 + w1; l_hi += w2 + w3;
+            const int col = warp * 16 + n * 8 + tq * 2;
+            *reinterpret_cast<uint32_t*>(sp + gq * LP + col) = sa_pack(w0, w1);
+            *reinterpret_cast<uint32_t*>(sp + (gq + 8) * LP + col) = sa_pack(w2, w3);
+        }
+        __syncthreads();
+        // this warp's VPW value columns over all 64 keys of the tile
+        const int cw = warp * VPW;
+#pragma unroll
+        for (int kk = 0; kk < TK / 16; kk++) {
+            uint32_t a[4];
+            sa_ldsm_x4(sp_a + (uint32_t)(((lane & 15) * LP + kk * 16 + (lane >> 4) * 8) * 2), a[0], a[1], a[2], a[3]);
+#pragma unroll
+            for (int n2 = 0; n2 < VPW / 16; n2++) {
+                if (cw + n2 * 16 >= DP) continue;                 // beyond the staged columns (ranks that are no multiple of 4 * VPW)
+                uint32_t b0, b1, b2, b3;
+                sa_ldsm_x4_t(sk_a + (uint32_t)(((kk * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * LK + cw + n2 * 16 + (lane >> 4) * 8) * 2), b0, b1, b2, b3);
+                sa_mma(o[2 * n2], a, b0, b1);
+                sa_mma(o[2 * n2 + 1], a, b2, b3);
+            }
+        }
+        __syncthreads();                                         // the tile and the weights may be overwritten
+    }
+    l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1); l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
+    l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1); l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);
+    if (tq == 0) { smx[warp * 16 + gq] = l_lo; smx[warp * 16 + gq + 8] = l_hi; }
+    __syncthreads();
+    if (threadIdx.x < nh) {
+        const int hh = threadIdx.x;
+        out[(size_t)hh * (b.vdim + 2) + 1] = (smx[hh] + smx[16 + hh]) + (smx[32 + hh] + smx[48 + hh]);
+    }
+    if (warp == 0 && tq == 0) {
+        if (gq < nh) out[(size_t)gq * (b.vdim + 2)] = m_lo;
+        if (gq + 8 < nh) out[(size_t)(gq + 8) * (b.vdim + 2)] = m_hi;
+    }
+    const int cw = warp * VPW;
+#pragma unroll
+    for (int n = 0; n < VPW / 8; n++)
+#pragma unroll
+        for (int x = 0; x < 2; x++) {
+            const int c = cw + n * 8 + tq * 2 + x;
+            if (c >= b.vdim) continue;
+            if (gq < nh) out[(size_t)gq * (b.vdim + 2) + 2 + c] = o[n][x];
+            if (gq + 8 < nh) out[(size_t)(gq + 8) * (b.vdim + 2) + 2 + c] = o[n][2 + x];
+        }
 }
 
 // Value up-projection of the summed latents and the head's gate: out[r][a_off + h vdim + v] = logistic(P[r][g_off + h]) * uv[h vdim + v] . ol[r][h]
