@@ -162,6 +162,18 @@ def test_passes_inside_a_step_cut_anywhere(lib):
     assert rel(a[:70], R.forward(cfg, W, t)) < TOL["float32"] and rel(a, b) < 1e-5
 
 
+def test_passes_of_the_tiled_path(lib):
+    """bfloat16, passes of 64 rows inside longer steps: every pass expands keys and values from the latents that earlier passes cached."""
+    cfg = NT.make_config(vocab=64, width=64, layers=[L(mlp=D(64)), L(heads=2, q_rank=16, window=90, mlp=E(4, 2, 32, 32))])
+    t = toks(5, 200, 64)
+    m1, W = make(lib, cfg, "bfloat16", seed=10, max_rows=64)
+    m2, _ = make(lib, cfg, "bfloat16", seed=10)
+    a = m1.step([(0, t), (1, t[:70])], range(270))
+    b = m2.step([(0, t), (1, t[:70])], range(270))
+    want = R.forward(cfg, W, t)
+    assert close(a[:200], want, "bfloat16", cfg) and close(a[200:], want[:70], "bfloat16", cfg) and close(a, b, "bfloat16", cfg)
+
+
 # ------------------------------------------------------------------ batches, slots
 @pytest.mark.parametrize("mode", ["float32", "bfloat16"])
 def test_batch_of_unequal_requests_equals_each_alone(lib, mode):
