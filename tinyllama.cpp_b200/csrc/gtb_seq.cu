@@ -529,7 +529,7 @@ int run_prenorm_layer(gtb_seq_model* m, const PassTables& t, int R, int S, const
     {
         const LatAttn a = lat_args(m, b);
         const int hd = a.dim + a.rope;
-        k_lat_prep<OT><<<R, 128, 0, st>>>(t, a, m->P, l.n1, (OT*)run.kc[0], (OT*)m->opQ, b.qrank_p);
+        k_lat_prep<OT><<<dim3(R, a.q_rank > 0 ? 2 : 1), 128, 0, st>>>(t, a, m->P, l.n1, (OT*)run.kc[0], (OT*)m->opQ, b.qrank_p);
         GTB_LAUNCHED();
         const float* Q = m->P;
         int ldq = l.n1, q0 = b.q_off;

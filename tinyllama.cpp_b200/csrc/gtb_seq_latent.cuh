@@ -170,8 +170,8 @@ __device__ __forceinline__ void rot_pair(const LatAttn& b, int pr, int& i0, int&
     i1 = b.rot_layout ? 2 * pr + 1 : pr + b.rot_dims / 2;
 }
 
-// per row: latent = unit-RMS(dkv[:rank]) * kv_norm and the rotated key part -> the slot's cache row; with a query latent,
-// unit-RMS(dq) * q_norm -> the operand of the query up-projection (zero-padded to ld_q)
+// per row: latent = unit-RMS(dkv[:rank]) * kv_norm and the rotated key part -> the slot's cache row (CTA y = 0); with a query latent,
+// unit-RMS(dq) * q_norm -> the operand of the query up-projection, zero-padded to ld_q (CTA y = 1)
 template <typename OT>
 __global__ void __launch_bounds__(128) k_lat_prep(PassTables t, LatAttn b, const float* __restrict__ P, int ldp, OT* __restrict__ cache,
                                                   OT* __restrict__ opq, int ld_q) {
@@ -179,6 +179,14 @@ __global__ void __launch_bounds__(128) k_lat_prep(PassTables t, LatAttn b, const
     const int r = blockIdx.x;
     const int slot = t.seg_slot[t.row_seg[r]], pos = t.row_pos[r];
     const float* p = P + (size_t)r * ldp;
+    if (blockIdx.y == 1) {                               // the query latent (grid y = 2 only with one)
+        float sq_ = 0.0f;
+        for (int i = threadIdx.x; i < b.q_rank; i += blockDim.x) { const float v = p[b.q_off + i]; sq_ += v * v; }
+        sq_ = block_sum(sq_, red);
+        const float sc = 1.0f / sqrtf(sq_ / (float)b.q_rank + b.eps);
+        for (int i = threadIdx.x; i < ld_q; i += blockDim.x) opq[(size_t)r * ld_q + i] = cvt<OT>(i < b.q_rank ? p[b.q_off + i] * sc * b.q_norm[i] : 0.0f);
+        return;
+    }
     OT* dst = cache + ((size_t)slot * b.max_ctx + pos) * b.c_ld;
     float ss = 0.0f;
     for (int i = threadIdx.x; i < b.rank; i += blockDim.x) { const float v = p[b.kv_off + i]; ss += v * v; }
@@ -196,13 +204,6 @@ __global__ void __launch_bounds__(128) k_lat_prep(PassTables t, LatAttn b, const
         dst[b.rank + i1] = cvt<OT>(kr[i1] * cs + kr[i0] * sn);
     }
     for (int i = b.rot_dims + threadIdx.x; i < b.rope; i += blockDim.x) dst[b.rank + i] = cvt<OT>(kr[i]);
-    if (b.q_rank > 0) {
-        ss = 0.0f;
-        for (int i = threadIdx.x; i < b.q_rank; i += blockDim.x) { const float v = p[b.q_off + i]; ss += v * v; }
-        ss = block_sum(ss, red);
-        sc = 1.0f / sqrtf(ss / (float)b.q_rank + b.eps);
-        for (int i = threadIdx.x; i < ld_q; i += blockDim.x) opq[(size_t)r * ld_q + i] = cvt<OT>(i < b.q_rank ? p[b.q_off + i] * sc * b.q_norm[i] : 0.0f);
-    }
 }
 
 // Prompt portions: the heads' queries with their rotated part turned to the row's position, and the heads' gate logits behind them:
@@ -327,18 +328,11 @@ __global__ void __launch_bounds__(128) k_lat_dec_mma(PassTables t, SoftAttn b, c
         if (threadIdx.x < nh) { out[(size_t)threadIdx.x * (b.vdim + 2)] = -INFINITY; out[(size_t)threadIdx.x * (b.vdim + 2) + 1] = 0.0f; }
         return;
     }
-    for (int e = threadIdx.x; e < 16 * DP; e += 128) {
-        const int hh = e / DP, i = e % DP;
-        sq[hh * LK + i] = __float2bfloat16_rn((hh < nh && i < D) ? QA[(size_t)r * ldqa + (size_t)(h0 + hh) * D + i] : 0.0f);
-    }
     const bf16* kbase = cache + ((size_t)slot * b.max_ctx + lo) * b.k_ld;
     const bool vec = (D % 8 == 0) && (b.k_ld % 8 == 0);
     const uint32_t sq_a = (uint32_t)__cvta_generic_to_shared(sq), sk_a = (uint32_t)__cvta_generic_to_shared(sk), sp_a = (uint32_t)__cvta_generic_to_shared(sp);
-    float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.0f, l_hi = 0.0f;
-    float o[VPW / 8][4];
-#pragma unroll
-    for (int n = 0; n < VPW / 8; n++) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.0f; }
-    for (int j0 = n_lo; j0 < n_hi; j0 += TK) {
+    // keys j0 .. of the range -> the tile in shared memory (asynchronous 16-byte copies when the cache rows allow them)
+    auto load_tile = [&](int j0) {
         const int nk = min(TK, n_hi - j0);
         if (vec) {
             for (int e = threadIdx.x; e < TK * (DP / 8); e += 128) {
@@ -346,14 +340,42 @@ __global__ void __launch_bounds__(128) k_lat_dec_mma(PassTables t, SoftAttn b, c
                 const bool ok = rr < nk && c8 < D;
                 sa_cp16(sk_a + (uint32_t)((rr * LK + c8) * 2), ok ? (const void*)(kbase + (size_t)(j0 + rr) * b.k_ld + c8) : (const void*)kbase, ok);
             }
-            asm volatile("cp.async.commit_group;" ::: "memory");
-            asm volatile("cp.async.wait_group 0;" ::: "memory");
         } else {
             for (int e = threadIdx.x; e < TK * DP; e += 128) {
                 const int rr = e / DP, i = e % DP;
                 sk[rr * LK + i] = (rr < nk && i < D) ? kbase[(size_t)(j0 + rr) * b.k_ld + i] : __float2bfloat16_rn(0.0f);
             }
         }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    load_tile(n_lo);                                     // in flight while the queries are staged
+    const float* qsrc = QA + (size_t)r * ldqa + (size_t)h0 * D;      // the group's heads are contiguous: nh x D floats
+    if (D % 4 == 0 && ldqa % 4 == 0) {
+        for (int e = threadIdx.x; e < 16 * (DP - D) + (16 - nh) * D; e += 128) {      // zero the padding: columns D .. DP of every row, rows nh .. 16
+            const int npc = 16 * (DP - D);
+            if (e < npc) sq[(e / (DP - D)) * LK + D + e % (DP - D)] = __float2bfloat16_rn(0.0f);
+            else sq[(nh + (e - npc) / D) * LK + (e - npc) % D] = __float2bfloat16_rn(0.0f);
+        }
+#pragma unroll 4
+        for (int e = threadIdx.x * 4; e < nh * D; e += 512) {
+            const float4 v = __ldg(reinterpret_cast<const float4*>(qsrc + e));
+            bf16* dst = sq + (e / D) * LK + e % D;
+            *reinterpret_cast<uint32_t*>(dst) = sa_pack(v.x, v.y);
+            *reinterpret_cast<uint32_t*>(dst + 2) = sa_pack(v.z, v.w);
+        }
+    } else {
+        for (int e = threadIdx.x; e < 16 * DP; e += 128) {
+            const int hh = e / DP, i = e % DP;
+            sq[hh * LK + i] = __float2bfloat16_rn((hh < nh && i < D) ? qsrc[(size_t)hh * D + i] : 0.0f);
+        }
+    }
+    float m_lo = -INFINITY, m_hi = -INFINITY, l_lo = 0.0f, l_hi = 0.0f;
+    float o[VPW / 8][4];
+#pragma unroll
+    for (int n = 0; n < VPW / 8; n++) { o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.0f; }
+    for (int j0 = n_lo; j0 < n_hi; j0 += TK) {
+        const int nk = min(TK, n_hi - j0);
+        asm volatile("cp.async.wait_group 0;" ::: "memory");
         __syncthreads();
         // scores of this warp's 16 keys for the 16 heads
         float sc[2][4] = {{0.0f, 0.0f, 0.0f, 0.0f}, {0.0f, 0.0f, 0.0f, 0.0f}};
@@ -411,6 +433,7 @@ __global__ void __launch_bounds__(128) k_lat_dec_mma(PassTables t, SoftAttn b, c
             }
         }
         __syncthreads();                                         // the tile and the weights may be overwritten
+        if (j0 + TK < n_hi) load_tile(j0 + TK);
     }
     l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 1); l_lo += __shfl_xor_sync(0xffffffffu, l_lo, 2);
     l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 1); l_hi += __shfl_xor_sync(0xffffffffu, l_hi, 2);

@@ -531,25 +531,44 @@ __global__ void __launch_bounds__(128) k_sattn_split(PassTables t, SoftAttn b, c
 template <typename OT>
 __global__ void __launch_bounds__(128) k_sattn_join(SoftAttn b, const float* __restrict__ P, int ldp, const float* __restrict__ part, int R, int splits,
                                                     OT* __restrict__ out, int ld_out) {
+    // splits <= 32: one warp fetches every split's maximum and denominator at once and turns them into the splits' weights; the value sums
+    // are then folded in order without waiting on a load per split
+    __shared__ float sw[32];
+    __shared__ float s_inv;
     const int r = blockIdx.x, h = blockIdx.y;
     const size_t stride = (size_t)R * b.heads * (b.vdim + 2);
     const float* p0 = part + ((size_t)r * b.heads + h) * (b.vdim + 2);
-    float M = b.sink ? b.sink[h] : -INFINITY;
-    for (int k = 0; k < splits; k++) M = fmaxf(M, p0[k * stride]);
-    float l = b.sink ? expf(b.sink[h] - M) : 0.0f;
-    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-    for (int k = 0; k < splits; k++) {
-        const float mk = p0[k * stride];
-        if (mk == -INFINITY) continue;
-        const float w = expf(mk - M);
-        l += p0[k * stride + 1] * w;
-#pragma unroll
-        for (int cc = 0; cc < 4; cc++) {
-            const int c = threadIdx.x + cc * blockDim.x;
-            if (c < b.vdim) acc[cc] = fmaf(p0[k * stride + 2 + c], w, acc[cc]);
-        }
+    if (threadIdx.x < 32) {
+        const int k = threadIdx.x;
+        const float mk = k < splits ? p0[k * stride] : -INFINITY, lk = k < splits ? p0[k * stride + 1] : 0.0f;
+        const float sink = b.sink ? b.sink[h] : -INFINITY;
+        const float M = fmaxf(sink, warp_max(mk));
+        const float w = mk == -INFINITY ? 0.0f : expf(mk - M);
+        float l = warp_sum(lk * w);
+        if (b.sink) l += expf(sink - M);
+        sw[k] = w;
+        if (k == 0) s_inv = 1.0f / l;
     }
-    sattn_store<OT>(b, P, ldp, r, h, 1.0f / l, acc, out, ld_out);
+    __syncthreads();
+    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    // eight splits at a time: all their loads are issued before the first multiply-add waits on one (sw is 0 beyond `splits`)
+    for (int k0 = 0; k0 < splits; k0 += 8) {
+        float v[8][4];
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            const bool on = sw[k0 + i] != 0.0f;          // an empty key range left its value sums unwritten
+#pragma unroll
+            for (int cc = 0; cc < 4; cc++) {
+                const int c = threadIdx.x + cc * blockDim.x;
+                v[i][cc] = (on && c < b.vdim) ? p0[(size_t)(k0 + i) * stride + 2 + c] : 0.0f;
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < 8; i++)
+#pragma unroll
+            for (int cc = 0; cc < 4; cc++) acc[cc] = fmaf(v[i][cc], sw[k0 + i], acc[cc]);
+    }
+    sattn_store<OT>(b, P, ldp, r, h, s_inv, acc, out, ld_out);
 }
 
 // ------------------------------------------------------------------------------------------------ PolyNorm
