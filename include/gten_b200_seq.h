@@ -26,9 +26,9 @@ extern "C" {
 
 enum { GTB_SEQ_BF16 = 0, GTB_SEQ_F32 = 1 };                       /* compute mode */
 enum { GTB_MIX_SIGMOID_ATTN = 1, GTB_MIX_RETENTION = 2, GTB_MIX_MINGRU = 3, GTB_MIX_SOFTMAX_ATTN = 4, GTB_MIX_LATENT_ATTN = 5 };   /* branch kinds of a token mixer */
-enum { GTB_BLOCK_PARALLEL = 0, GTB_BLOCK_POSTNORM = 1, GTB_BLOCK_PRENORM = 2 };          /* layer styles */
-enum { GTB_FF_GEGLU = 0, GTB_FF_POLYNORM = 1, GTB_FF_EXPERTS = 2, GTB_FF_GATED_EXPERTS = 3 };   /* feed-forward kinds */
-enum { GTB_NORM_RMS = 0, GTB_NORM_DYT = 1 };                      /* norm of a pre-norm layer and of the model's output */
+enum { GTB_BLOCK_PARALLEL = 0, GTB_BLOCK_POSTNORM = 1, GTB_BLOCK_PRENORM = 2, GTB_BLOCK_SANDWICH = 3 };   /* layer styles */
+enum { GTB_FF_GEGLU = 0, GTB_FF_POLYNORM = 1, GTB_FF_EXPERTS = 2, GTB_FF_GATED_EXPERTS = 3, GTB_FF_SWIGLU = 4, GTB_FF_GROUP_EXPERTS = 5 };   /* feed-forward kinds */
+enum { GTB_NORM_RMS = 0, GTB_NORM_DYT = 1, GTB_NORM_LAYER = 2 };          /* norm of a pre-norm / sandwich layer and of the model's output */
 enum { GTB_ROT_HALVES = 0, GTB_ROT_INTERLEAVED = 1 };             /* which entries a rotary pair takes: (i, i + dims/2) or (2i, 2i + 1) */
 
 /* One branch of a token mixer.  Tensors of branch b of layer i are "l<i>.mix.<name>.{q,k,v,o,...}".
@@ -56,7 +56,18 @@ enum { GTB_ROT_HALVES = 0, GTB_ROT_INTERLEAVED = 1 };             /* which entri
  *    q_rot . k_rot).  q_rank > 0: q = uq (unit-RMS(dq h) * dq.norm) instead of q h.  Rotation on the first rot_dims (<= rope_dim)
  *    entries of the rotated part in rot_layout.  window, sink as for GTB_MIX_SOFTMAX_ATTN (no pooled blocks); gated 3: head a's output
  *    times logistic(g h)_a, g with one row per head.  The slot caches only c and the rotated key part ([kv_rank + rope_dim] per token).
- *    Tensors q | dq, dq.norm, uq; dkv, dkv.norm, uk, uv, sink, g, o. */
+ *    Tensors q | dq, dq.norm, uq; dkv, dkv.norm, uk, uv, sink, g, o.
+ *  In sandwich layers (GTB_BLOCK_SANDWICH) GTB_MIX_SOFTMAX_ATTN and GTB_MIX_RETENTION take further parameters:
+ *    softmax attention -- qk_norm 3: ONE RMS norm over the whole q projection (and one over the whole k projection) with weights q.norm
+ *    [heads * maps * dim], k.norm [kv_heads * maps * dim]; rot_divide > 0: every rotary frequency is divided by it; chunk > 0: position i
+ *    sees j <= i only when floor(i / chunk) = floor(j / chunk); gated 3: one logistic gate per head (g [heads][width]); bias: q, k, v
+ *    projections add the vectors q.b, k.b, v.b; out_scale weighs the branch.  maps 2 (differential attention): every head has two query
+ *    parts and every K/V head two key parts of `dim` entries ([part 1 | part 2] per head), each pair a softmax attention of its own over
+ *    the same values; with lambda = exp(lq1 . lk1) - exp(lq2 . lk2) + diff (tensors lq1, lk1, lq2, lk2 [dim]) the head's output is
+ *    (a1 - lambda a2) scaled to unit RMS over its vdim entries (eps of the model) times (1 - diff), then gated.  The cache of a maps-2 layer
+ *    holds both key parts; kv_from names a layer of the same style with the same kv_heads, maps, dim, vdim.
+ *    retention -- act 1: q, k, v <- silu(q), silu(k), silu(v) before the recurrence; out_norm 2: the concatenated heads are scaled to
+ *    unit RMS TOGETHER and multiplied by the weight `norm` [heads * vdim]; gated 2: times logistic(g h). */
 typedef struct {
     int kind;
     char name[16];
@@ -75,6 +86,12 @@ typedef struct {
     int sink;                        /* 1: learned per-head sink in the softmax denominator */
     int kv_from;                     /* -1: own keys and values */
     int rope_dim, kv_rank, q_rank;   /* GTB_MIX_LATENT_ATTN */
+    int chunk;                       /* > 0: keys of the query's own chunk of positions only */
+    int maps;                        /* 0 / 1: plain softmax attention; 2: differential attention */
+    float diff;                      /* maps 2: the constant in lambda and in the output factor (1 - diff) */
+    int bias;                        /* 1: q, k, v projections have bias vectors */
+    int act;                         /* retention: 1 = silu on q, k, v */
+    float rot_divide;                /* > 0: rotary frequencies are divided by it */
 } gtb_seq_branch;
 
 /* Tensors of layer i beyond its branches'.  Parallel blocks: "l<i>.norm1" (one gain), "l<i>.mlp.{gate,up,down}", "l<i>.canon{1,2}".
@@ -96,17 +113,29 @@ typedef struct {
                                       * GTB_BLOCK_PRENORM: x += mixer(norm1(x)); x += ff(norm2(x)), norm of kind norm_kind; with config.streams > 0
                                       * the stream is kept in `streams` copies: sublayer q reads u = sum_s hc<q>.in[s] x_s and all copies are
                                       * rewritten at once from the old ones, x_t <- sum_s hc<q>.mix[s][t] x_s + hc<q>.out[t] y.  One branch
-                                      * (GTB_MIX_LATENT_ATTN) */
+                                      * (GTB_MIX_LATENT_ATTN);
+                                      * GTB_BLOCK_SANDWICH: x += norm1b(mixer(norm1(x))); x += norm2b(ff(norm2(x))), four norms of kind norm_kind
+                                      * (GTB_NORM_LAYER or GTB_NORM_RMS with a plain weight); one or two branches (GTB_MIX_SOFTMAX_ATTN,
+                                      * GTB_MIX_RETENTION), each weighted by its out_scale */
     int ff_kind;                     /* GTB_FF_GEGLU: down(gelu_tanh(gate h) * (up h)); GTB_FF_POLYNORM: down(a N(z) + b N(z^2) + c N(z^3) + e),
                                       * z = up h, N = unit RMS over the ff values, (a, b, c, e) = tensor mlp.act; GTB_FF_EXPERTS: router outputs
                                       * 0 .. experts-1 are experts e<i>.down(relu(e<i>.up h)^2), the `identity` outputs after them return h;
                                       * s = softmax(router h), the `top` largest s + correction are chosen and weighted with their s;
                                       * GTB_FF_GATED_EXPERTS: experts e<i>.down(silu(e<i>.gate h) * (e<i>.up h)); s = logistic(router h) in fp32, the
                                       * `top` largest s are chosen (ties to the lower index) and weighted with s / (sum of the chosen s + 1e-20);
-                                      * shared_ff > 0: an expert of that inner width runs for every row, times logistic(shared.sg h) */
+                                      * shared_ff > 0: an expert of that inner width runs for every row, times logistic(shared.sg h);
+                                      * GTB_FF_SWIGLU: down(silu(gate h) * (up h));
+                                      * GTB_FF_GROUP_EXPERTS: experts e<i>.down(relu(e<i>.up h)^2); s = logistic(router h) in fp32; the experts form
+                                      * route_groups equal groups of neighbours, a group ranks by the sum of its two largest s, only experts of the
+                                      * route_keep best groups can be chosen; the `top` largest s among them are chosen (ties to the lower index) and
+                                      * weighted with route_scale * s (not renormalised); shared_ff > 0: one more expert of the same form and that
+                                      * inner width runs for every row with weight 1 */
     int experts, top, identity;
-    int norm_kind;                   /* GTB_BLOCK_PRENORM: GTB_NORM_RMS (x / rms(x) * w) or GTB_NORM_DYT (tanh(alpha x) * w + b, no statistics) */
+    int norm_kind;                   /* GTB_BLOCK_PRENORM: GTB_NORM_RMS (x / rms(x) * w) or GTB_NORM_DYT (tanh(alpha x) * w + b, no statistics);
+                                      * GTB_BLOCK_SANDWICH: GTB_NORM_RMS or GTB_NORM_LAYER ((x - mean) / sqrt(variance + eps) * w + b) */
     int shared_ff;
+    int route_groups, route_keep;    /* GTB_FF_GROUP_EXPERTS (0 groups counts as 1, 0 kept as all) */
+    float route_scale;
 } gtb_seq_layer;
 
 typedef struct {
@@ -119,7 +148,8 @@ typedef struct {
     int n_slots, max_ctx;            /* sequences held at once; positions per slot */
     int max_rows;                    /* rows per pass over the weights (longer steps are cut into passes); 0: default */
     float embed_scale;               /* embedding rows are multiplied by this (0 counts as 1) */
-    int final_norm;                  /* 0: one gain; 1: weight vector stored around zero (1 + w); 2: Dynamic Tanh, tensors final.norm, final.norm.alpha, final.norm.b */
+    int final_norm;                  /* 0: one gain; 1: weight vector stored around zero (1 + w); 2: Dynamic Tanh, tensors final.norm, final.norm.alpha, final.norm.b;
+                                      * 3: layer norm, tensors final.norm, final.norm.b */
     int streams;                     /* pre-norm layers: copies of the residual stream under hyper-connections (all equal to the embedding output at
                                       * the start, summed at the end); 0: one stream, plain residual sum */
     float logit_softcap;             /* > 0: logits <- cap * tanh(logits / cap) */

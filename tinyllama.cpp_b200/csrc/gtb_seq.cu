@@ -15,6 +15,11 @@
 //    boundary applies the finished sublayer's update to all copies and forms the next sublayer's normalised input.  Latent attention
 //    caches [latent | rotated key part] per token ([n_slots][max_ctx][c_ld]); gated experts store [gate | up] of every expert as one
 //    block of 2 ff rows ([experts][2 ff][width]), the shared expert's gate as one more row of the router matrix.
+//  * sandwich layers (GTB_BLOCK_SANDWICH) run like post-norm layers with a norm on both sides of each sublayer: one kernel per sublayer
+//    boundary adds norm_b(sublayer output) to the stream and writes the next sublayer's normalised input.  Their mixers are the branch
+//    kernels of the other styles (softmax attention, retention) side by side, each weighted by out_scale in the out-projection operand.
+//    Group-limited experts reuse the stacked layout of the post-norm experts; the shared expert is cut along its inner width into parts of
+//    one expert's size that follow the routed experts in the same stacks, so every row simply has `top + parts` choices.
 #include <math.h>
 #include <string.h>
 
@@ -30,6 +35,7 @@
 #include "gtb_seq_mixers.cuh"
 #include "gtb_seq_mixers_tiled.cuh"
 #include "gtb_seq_latent.cuh"
+#include "gtb_seq_sandwich.cuh"
 
 using namespace gtb;
 using namespace gtb::seq;
@@ -46,6 +52,8 @@ struct TensorDest {
     int ld = 0;                // destination row stride in elements (matrix)
     bool scalar = false;       // shape []
     int group = 0, group_stride = 0;   // matrix rows placed in groups of `group` rows, `group_stride` rows apart (0: contiguous)
+    int split_cols = 0;                // > 0: columns placed in blocks of split_cols, block j at dst + j * split_stride elements
+    size_t split_stride = 0;
     bool loaded = false;
 };
 
@@ -62,6 +70,9 @@ struct BranchW {
     bf16 *w_uq = nullptr, *w_uk = nullptr, *w_uv = nullptr;
     float* d_kvnorm = nullptr;
     int kv_off = 0, c_ld = 0, rank_p = 0, qrank_p = 0;
+    // sandwich layers
+    float* d_onorm = nullptr;                       // retention: weight of the norm over the concatenated heads
+    float* d_lam[4] = {nullptr, nullptr, nullptr, nullptr};     // differential attention: lq1, lk1, lq2, lk2
 };
 
 struct LayerW {
@@ -86,6 +97,9 @@ struct LayerW {
     bf16 *w_sh_gu = nullptr, *w_sh_down = nullptr;                      // shared expert
     int sff = 0, sff_p = 0;
     bool sh_inter = false, e_inter = false;                             // [gate | up] rows interleaved in groups of 32
+    // sandwich style
+    float *sn_w[4] = {nullptr, nullptr, nullptr, nullptr}, *sn_b[4] = {nullptr, nullptr, nullptr, nullptr};     // norm1, norm1b, norm2, norm2b
+    int n_sh = 0, e_total = 0;                                          // parts of the shared expert; routed experts + parts
 };
 
 struct Run {
@@ -113,7 +127,8 @@ struct gtb_seq_model {
     float *loop_step = nullptr, *final_gain = nullptr, *final_b = nullptr, *final_a = nullptr;
     // pre-norm style: copies of the stream, latent attention workspace, shared expert
     int ns = 1;                                  // copies of the stream
-    bool prenorm = false;
+    bool prenorm = false, sandwich = false;
+    float* qk_sc = nullptr;                      // scales of the whole-projection q / k norm [max_rows][2]
     float *xs = nullptr, *hc_one = nullptr, *latQ = nullptr, *latQA = nullptr, *Y2 = nullptr, *shw = nullptr;
     void *opQ = nullptr, *opO = nullptr;
     float* latX = nullptr;                       // expanded [plain keys | values] of one segment's visible range, fp32 [max_ctx][heads * (dim + vdim)]
@@ -286,18 +301,19 @@ RetLaunch ret_launch(const gtb_seq_branch& d) {
 
 template <int DP, int VP>
 int launch_sattn_mma(const PassTables& t, const SoftAttn& a, int S, int n_tiles, const float* P, int ldp, const bf16* kc, const bf16* vc, const float* pk, const float* pv,
-                     bf16* out, int ld_out) {
+                     bf16* out, int ld_out, float* out_f, int ld_f) {
     const size_t smem = (3 * 64 * (size_t)(DP + 8) + 2 * 64 * (size_t)(VP + 8)) * 2;      // queries + two stages of keys and values
     static bool attr = false;
     if (!attr) { GTB_CUDA(cudaFuncSetAttribute(k_sattn_mma<DP, VP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem)); attr = true; }
-    k_sattn_mma<DP, VP><<<dim3(n_tiles, a.heads), 128, smem, ctx().stream>>>(t, a, S, P, ldp, kc, vc, pk, pv, out, ld_out);
+    k_sattn_mma<DP, VP><<<dim3(n_tiles, a.heads * sa_maps(a)), 128, smem, ctx().stream>>>(t, a, S, P, ldp, kc, vc, pk, pv, out, ld_out, out_f, ld_f);
     GTB_LAUNCHED();
     return GTB_OK;
 }
+// out_f != null: the units' outputs go there in fp32 ([rows][ld_f], unit-major) without gate or weight instead of `out`
 int sattn_mma(const PassTables& t, const SoftAttn& a, int S, int n_tiles, const float* P, int ldp, const bf16* kc, const bf16* vc, const float* pk, const float* pv,
-              bf16* out, int ld_out) {
+              bf16* out, int ld_out, float* out_f = nullptr, int ld_f = 0) {
     const int dp = a.dim <= 32 ? 32 : a.dim <= 64 ? 64 : 128, vp = a.vdim <= 32 ? 32 : a.vdim <= 64 ? 64 : 128;
-#define SA_CASE(D, V) if (dp == D && vp == V) return launch_sattn_mma<D, V>(t, a, S, n_tiles, P, ldp, kc, vc, pk, pv, out, ld_out)
+#define SA_CASE(D, V) if (dp == D && vp == V) return launch_sattn_mma<D, V>(t, a, S, n_tiles, P, ldp, kc, vc, pk, pv, out, ld_out, out_f, ld_f)
     SA_CASE(32, 32); SA_CASE(32, 64); SA_CASE(32, 128); SA_CASE(64, 32); SA_CASE(64, 64); SA_CASE(64, 128); SA_CASE(128, 32); SA_CASE(128, 64); SA_CASE(128, 128);
 #undef SA_CASE
     return -1;
@@ -317,6 +333,8 @@ SoftAttn soft_args(const gtb_seq_model* m, const BranchW& b, const Run& run) {
     a.window = b.d.window; a.pool = (b.d.window > 0) ? b.d.pool : 0; a.sink = b.d_sink; a.gate = b.d.gated;
     a.q_off = b.q_off; a.k_off = b.k_off; a.v_off = b.v_off; a.g_off = b.g_off; a.a_off = b.a_off;
     a.own_kv = b.d.kv_from < 0; a.max_ctx = m->cfg.max_ctx; a.max_blocks = run.max_blocks;
+    a.maps = b.d.maps > 1 ? b.d.maps : 1; a.chunk = b.d.chunk; a.out_scale = b.d.out_scale; a.qk_sc = m->qk_sc;
+    if (a.maps > 1) { a.gate = 0; a.out_scale = 1.0f; }       // the maps are combined, gated and weighted afterwards
     return a;
 }
 
@@ -439,6 +457,201 @@ int run_postnorm_layer(gtb_seq_model* m, const PassTables& t, int R, int S, cons
         GTB_CUDA(cudaMemsetAsync(m->Y, 0, (size_t)R * W * sizeof(float), st));
     }
     k_postnorm_add<OT><<<R, 256, 0, st>>>(m->Y, W, c.eps, l.norm2, m->sel_idx, m->sel_w, top, E, nullptr, nullptr, m->x, opA, wp, RouteNext{});
+    GTB_LAUNCHED();
+    return GTB_OK;
+}
+
+// One retention branch on R rows: projections in m->P, output into the out-projection operand.  Prompt portions run chunk-wise, everything
+// else row by row from the slot's state.
+template <typename OT>
+int run_retention(gtb_seq_model* m, const PassTables& t, int R, int S, const Run& run, int bi, const LayerW& l, bool portions, const int* seg_lens) {
+    cudaStream_t st = ctx().stream;
+    const BranchW& b = l.br[bi];
+    OT* opC = (OT*)m->opC;
+    const RetBranch a = ret_args(m, b);
+    const RetChunk rcfg = ret_chunk(b.d);
+    const bool chunks = portions && rcfg.ok;
+    if (b.d.act) {
+        // in place, in one pass over q | k | v (neighbours in the projection): activating inside the chunk kernels instead was measured
+        // slower (they read q and k twice; 41 us more in them against 23 us for this kernel at 2048 rows x 8 heads of 128)
+        const int n = b.v_off + a.heads * a.vdim - b.q_off;
+        k_silu_cols<<<(unsigned)(((size_t)R * n + 255) / 256), 256, 0, st>>>(m->P, l.n1, b.q_off, n, R);
+        GTB_LAUNCHED();
+    }
+    auto post = [&]() -> int {
+        if (b.d.out_norm == 2) k_ret_post_all<OT><<<R, 256, 0, st>>>(a, b.d_onorm, m->O, m->P, l.n1, opC, l.kout_p);
+        else k_ret_post<OT><<<dim3(R, (a.heads + 3) / 4), 128, 0, st>>>(a, m->O, m->P, l.n1, opC, l.kout_p);
+        GTB_LAUNCHED();
+        return GTB_OK;
+    };
+    if (chunks) {
+        int n_chunks = 0;
+        for (int s = 0; s < S; s++) n_chunks += (seg_lens[s] + rcfg.C - 1) / rcfg.C;
+        const size_t need = (size_t)n_chunks * a.heads * a.dim * a.vdim;
+        if (need > m->retU_floats) return gtb::fail(GTB_ERR_STATE, "chunk workspace too small (%zu > %zu floats)", need, m->retU_floats);
+        const int nvs = (a.vdim + rcfg.vs - 1) / rcfg.vs;
+        if (a.rot_dims > 0 || a.scale != 1.0f) {
+            k_ret_rotate<<<R, 128, 0, st>>>(t, a, m->P, l.n1);
+            GTB_LAUNCHED();
+        }
+        if (rcfg.smem_kv > 48 * 1024) GTB_CUDA(cudaFuncSetAttribute(k_ret_chunk_kv, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)rcfg.smem_kv));
+        k_ret_chunk_kv<<<dim3(n_chunks, a.heads, nvs), 256, rcfg.smem_kv, st>>>(t, a, m->P, l.n1, S, rcfg.C, rcfg.vs, m->retU);
+        GTB_LAUNCHED();
+        k_ret_scan<<<dim3(S, a.heads, (a.dim * a.vdim + 255) / 256), 256, 0, st>>>(t, a, S, rcfg.C, m->retU, run.state[bi]);
+        GTB_LAUNCHED();
+        if (rcfg.smem_out > 48 * 1024) GTB_CUDA(cudaFuncSetAttribute(k_ret_chunk_out, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)rcfg.smem_out));
+        k_ret_chunk_out<<<dim3(n_chunks, a.heads, nvs), 256, rcfg.smem_out, st>>>(t, a, m->P, l.n1, S, rcfg.C, rcfg.vs, m->retU, m->O);
+        GTB_LAUNCHED();
+        return post();
+    }
+    const RetLaunch rl = ret_launch(b.d);
+    if (rl.smem > 48 * 1024) GTB_CUDA(cudaFuncSetAttribute(k_retention, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)rl.smem));
+    k_retention<<<dim3(S, a.heads, rl.nvs), rl.block, rl.smem, st>>>(t, a, m->P, l.n1, run.state[bi], m->O, rl.vs);
+    GTB_LAUNCHED();
+    return post();
+}
+
+// ---- sandwich layers ---------------------------------------------------------------------------------------------------------
+NormArgs sw_norm(const gtb_seq_model* m, const LayerW& l, int q) {          // q: 0 norm1, 1 norm1b, 2 norm2, 3 norm2b
+    NormArgs n{};
+    n.kind = l.d.norm_kind; n.w = l.sn_w[q]; n.b = l.sn_b[q]; n.eps = m->cfg.eps;
+    return n;
+}
+
+// One softmax-attention branch of a sandwich layer on R rows: projections in m->P, output into the out-projection operand.
+template <typename OT>
+int run_soft_branch(gtb_seq_model* m, const PassTables& t, int R, int S, const Run& run, int bi, const LayerW& l, bool portions, int n_qtiles) {
+    cudaStream_t st = ctx().stream;
+    const gtb_seq_config& c = m->cfg;
+    const BranchW& b = l.br[bi];
+    OT* opC = (OT*)m->opC;
+    const SoftAttn a = soft_args(m, b, run);
+    const int M = a.maps, units = a.heads * M, nk = a.own_kv ? a.kv_heads * M : 0;
+    if (a.qk_norm == 3) {
+        k_proj_rms<<<R, 256, 0, st>>>(m->P, l.n1, a.q_off, units * a.dim, a.k_off, nk * a.dim, c.eps, m->qk_sc);
+        GTB_LAUNCHED();
+    }
+    k_sattn_prep<OT><<<dim3(R, (units + nk + (a.own_kv ? a.kv_heads : 0) + 3) / 4), 128, 0, st>>>(t, a, m->P, l.n1, (OT*)run.kc[bi], (OT*)run.vc[bi]);
+    GTB_LAUNCHED();
+    // two maps per head: the units' outputs stay fp32 (their difference is taken afterwards), unit-major in m->O
+    float* of = M > 1 ? m->O : nullptr;
+    const int ldf = units * a.vdim;
+    SoftAttn af = a;
+    af.a_off = 0;
+    const size_t smem = (a.dim + 128 + 33) * sizeof(float);
+    int done = -1;
+    if (portions && sizeof(OT) == 2 && a.dim <= 128 && a.vdim <= 128)
+        done = sattn_mma(t, a, S, n_qtiles, m->P, l.n1, (const bf16*)run.kc[bi], (const bf16*)run.vc[bi], nullptr, nullptr, (bf16*)opC, l.kout_p, of, ldf);
+    if (done > 0) return done;
+    if (done < 0 && !portions && R <= SPLIT_MAX_ROWS && m->sattn_part) {
+        int max_keys = c.max_ctx;
+        if (a.window > 0) max_keys = std::min(max_keys, a.window);
+        if (a.chunk > 0) max_keys = std::min(max_keys, a.chunk);
+        const int splits = std::max(1, std::min(32, (max_keys + 127) / 128));
+        if (splits > 1) {
+            k_sattn_split<OT><<<dim3(R, units, splits), 128, smem, st>>>(t, a, m->P, l.n1, (const OT*)run.kc[bi], (const OT*)run.vc[bi], nullptr, nullptr, m->sattn_part, R);
+            GTB_LAUNCHED();
+            if (of) k_sattn_join<float><<<dim3(R, units), 128, 0, st>>>(af, m->P, l.n1, m->sattn_part, R, splits, of, ldf);
+            else k_sattn_join<OT><<<dim3(R, units), 128, 0, st>>>(a, m->P, l.n1, m->sattn_part, R, splits, opC, l.kout_p);
+            GTB_LAUNCHED();
+            done = 0;
+        }
+    }
+    if (done < 0) {
+        if (of) k_sattn<OT, float><<<dim3(R, units), 128, smem, st>>>(t, af, m->P, l.n1, (const OT*)run.kc[bi], (const OT*)run.vc[bi], nullptr, nullptr, of, ldf);
+        else k_sattn<OT, OT><<<dim3(R, units), 128, smem, st>>>(t, a, m->P, l.n1, (const OT*)run.kc[bi], (const OT*)run.vc[bi], nullptr, nullptr, opC, l.kout_p);
+        GTB_LAUNCHED();
+    }
+    if (of) {
+        DiffArgs d{};
+        d.heads = a.heads; d.dim = a.dim; d.vdim = a.vdim; d.diff = b.d.diff; d.eps = c.eps; d.out_scale = b.d.out_scale != 0.0f ? b.d.out_scale : 1.0f;
+        d.lq1 = b.d_lam[0]; d.lk1 = b.d_lam[1]; d.lq2 = b.d_lam[2]; d.lk2 = b.d_lam[3];
+        d.gate = b.d.gated; d.g_off = b.g_off; d.a_off = b.a_off;
+        k_diff_combine<OT><<<dim3(R, (a.heads + 3) / 4), 128, 0, st>>>(d, of, m->P, l.n1, opC, l.kout_p);
+        GTB_LAUNCHED();
+    }
+    return GTB_OK;
+}
+
+// One layer of the sandwich style on R rows: x += norm1b(mixer(norm1(x))); x += norm2b(ff(norm2(x))).  opA holds norm1(x) on entry; on
+// return it holds `next` of the new stream (the following layer's norm1) when next.w is set.
+template <typename OT>
+int run_sandwich_layer(gtb_seq_model* m, const PassTables& t, int R, int S, const Run& run, const LayerW& l, bool portions, const int* seg_lens, int n_qtiles,
+                       const NormArgs& next) {
+    cudaStream_t st = ctx().stream;
+    const gtb_seq_config& c = m->cfg;
+    const int W = c.width, wp = m->wp;
+    OT *opA = (OT*)m->opA, *opC = (OT*)m->opC;
+    int rc = product<OT>(m, opA, wp, l.w_mix, wp, m->P, l.n1, R, l.n1, wp, l.d_bias, 0);
+    if (rc) return rc;
+    for (int bi = 0; bi < l.d.n_branches; bi++) {
+        if (l.br[bi].d.kind == GTB_MIX_SOFTMAX_ATTN) rc = run_soft_branch<OT>(m, t, R, S, run, bi, l, portions, n_qtiles);
+        else rc = run_retention<OT>(m, t, R, S, run, bi, l, portions, seg_lens);
+        if (rc) return rc;
+    }
+    rc = product<OT>(m, opC, l.kout_p, l.w_out, l.kout_p, m->Y, W, R, W, l.kout_p, nullptr, 0);
+    if (rc) return rc;
+    // few rows and a routed feed-forward next: the residual update also computes the router's logits from the operand row it has just formed
+    // and picks the experts (two launches less per layer on a decode step)
+    GroupRouteNext rn{};
+    const int groups = std::max(1, l.d.route_groups), keep = l.d.route_keep > 0 ? l.d.route_keep : groups;
+    const bool routed = l.ff > 0 && l.d.ff_kind == GTB_FF_GROUP_EXPERTS;
+    const size_t rn_smem = routed ? ((size_t)W + 3 * l.d.experts + groups) * sizeof(float) : 0;
+    if (routed && R <= 8 && rn_smem <= 40 * 1024) {
+        rn.w = l.w_router; rn.ldw = wp; rn.n_exp = l.d.experts; rn.n_groups = groups; rn.keep = keep; rn.top = l.d.top; rn.n_always = l.n_sh; rn.scale = l.d.route_scale;
+        rn.sel_idx = m->sel_idx; rn.sel_w = m->sel_w;
+    }
+    k_sandwich_add<OT><<<R, 256, rn.w ? rn_smem : 0, st>>>(m->Y, nullptr, nullptr, nullptr, 0, W, sw_norm(m, l, 1), m->x, l.ff > 0 ? sw_norm(m, l, 2) : next, opA, wp, rn);
+    GTB_LAUNCHED();
+    if (l.ff == 0) return GTB_OK;
+    if (l.d.ff_kind == GTB_FF_SWIGLU) {
+        bool act_done = false;
+        if (sizeof(OT) == 2 && m->use_tensor && m->gp && R >= m->tensor_min_rows && l.gu_inter) {
+            rc = seq_gemm_bf16_gated(m->gp, opA, wp, l.w_gu, wp, opC, l.kfp, 0, R, 2 * l.ff, wp, 1, nullptr);
+            if (rc > 0) return rc;
+            if (rc == 0) { ctx().launches++; act_done = true; }
+        }
+        if (!act_done) {
+            rc = product<OT>(m, opA, wp, l.w_gu, wp, m->G, 2 * l.ff, R, 2 * l.ff, wp, nullptr, 0);
+            if (rc) return rc;
+            k_swiglu_rows<OT><<<dim3(R, std::max(1, std::min((l.kfp + 255) / 256, std::max(1, 2048 / R)))), 256, 0, st>>>(m->G, l.ff, l.gu_inter ? 1 : 0, nullptr, opC, l.kfp);
+            GTB_LAUNCHED();
+        }
+        rc = product<OT>(m, opC, l.kfp, l.w_down, l.kfp, m->Y, W, R, W, l.kfp, nullptr, 0);
+        if (rc) return rc;
+        k_sandwich_add<OT><<<R, 256, 0, st>>>(m->Y, nullptr, nullptr, nullptr, 0, W, sw_norm(m, l, 3), m->x, next, opA, wp, GroupRouteNext{});
+        GTB_LAUNCHED();
+        return GTB_OK;
+    }
+    // group-limited experts; the parts of the shared expert are choices top .. top + n_sh - 1 of every row
+    const int E = l.d.experts, Et = l.e_total, top = l.d.top + l.n_sh;
+    if (!rn.w) {
+        rc = product<OT>(m, opA, wp, l.w_router, wp, m->rl, E, R, E, wp, nullptr, 0);
+        if (rc) return rc;
+        k_moe_route_grouped<<<R, 32, (2 * E + groups) * sizeof(float), st>>>(m->rl, E, E, groups, keep, l.d.top, l.d.route_scale, l.n_sh, m->sel_idx, m->sel_w);
+        GTB_LAUNCHED();
+    }
+    const int n_pairs = R * top, mpad = (n_pairs + 127) / 128 * 128 + Et * 128;
+    if (sizeof(OT) == 2 && m->grouped_experts && m->use_tensor && m->gp && m->Xg && R >= m->tensor_min_rows && mpad <= m->mpad_max) {
+        k_moe_group<<<1, 1024, 2 * Et * sizeof(int), st>>>(m->sel_idx, n_pairs, Et, m->pair_dst, m->tile_e, mpad / 128);
+        GTB_LAUNCHED();
+        k_moe_gather<<<n_pairs, 128, 0, st>>>((const bf16*)opA, wp, top, m->pair_dst, m->sel_w, m->Xg, m->rw);
+        GTB_LAUNCHED();
+        rc = seq_gemm_bf16_grouped(m->gp, m->Xg, wp, l.w_up, wp, mpad, l.ff, wp, Et, m->tile_e, nullptr, 0, m->actg, l.kfp, m->rw);
+        if (rc == 0) rc = seq_gemm_bf16_grouped(m->gp, m->actg, l.kfp, l.w_down, l.kfp, mpad, W, l.kfp, Et, m->tile_e, m->Yg, W, nullptr, 0, nullptr);
+        if (rc > 0) return rc;
+        if (rc == 0) {
+            k_sandwich_add<OT><<<R, 256, 0, st>>>(nullptr, nullptr, m->Yg, m->pair_dst, top, W, sw_norm(m, l, 3), m->x, next, opA, wp, GroupRouteNext{});
+            GTB_LAUNCHED();
+            return GTB_OK;
+        }
+    }
+    const int cta_budget = std::max(1, 4096 / std::max(1, R * top));
+    k_moe_up_rows<OT><<<dim3(R * top, std::max(1, std::min(cta_budget, (l.kfp + 7) / 8))), 256, 0, st>>>(opA, wp, wp, l.w_up, wp, l.ff, l.kfp, Et, top, m->sel_idx, m->sel_w, (OT*)m->act);
+    GTB_LAUNCHED();
+    k_moe_down_rows<OT><<<dim3(R, std::max(1, std::min(std::max(1, 4096 / R), (W + 7) / 8))), 256, 0, st>>>((const OT*)m->act, l.kfp, l.w_down, W, Et, top, m->sel_idx, m->Y, W);
+    GTB_LAUNCHED();
+    k_sandwich_add<OT><<<R, 256, 0, st>>>(m->Y, nullptr, nullptr, nullptr, 0, W, sw_norm(m, l, 3), m->x, next, opA, wp, GroupRouteNext{});
     GTB_LAUNCHED();
     return GTB_OK;
 }
@@ -643,7 +856,7 @@ int run_prenorm_layer(gtb_seq_model* m, const PassTables& t, int R, int S, const
         if (!act_done) {
             rc = product<OT>(m, opA, wp, l.w_sh_gu, wp, m->G, 2 * l.sff, R, 2 * l.sff, wp, nullptr, 0);
             if (rc) return rc;
-            k_swiglu_rows<OT><<<R, 256, 0, st>>>(m->G, l.sff, l.sh_inter ? 1 : 0, m->shw, opC, l.sff_p);
+            k_swiglu_rows<OT><<<dim3(R, std::max(1, std::min((l.sff_p + 255) / 256, std::max(1, 2048 / R)))), 256, 0, st>>>(m->G, l.sff, l.sh_inter ? 1 : 0, m->shw, opC, l.sff_p);
             GTB_LAUNCHED();
         }
         rc = product<OT>(m, opC, l.sff_p, l.w_sh_down, l.sff_p, m->Y2, W, R, W, l.sff_p, nullptr, 0);
@@ -692,14 +905,34 @@ int run_pass(gtb_seq_model* m, const PassTables& t, int R, int S, bool from_pend
     k_plan<<<(R + 127) / 128, 128, 0, st>>>(t, R, from_pending ? 1 : 0);
     GTB_LAUNCHED();
     const bool first_reads_x = m->L[m->runs[0].layer].d.style == GTB_BLOCK_POSTNORM;
-    k_embed<OT><<<R, 256, 0, st>>>(t, m->embed, m->bigram, c.bigram_buckets, c.bigram_mul_prev, c.bigram_mul_cur, W, c.embed_scale != 0.0f ? c.embed_scale : 1.0f,
-                                   m->prenorm ? m->xs : m->x, c.loop_times > 0 ? m->x0 : nullptr, first_reads_x ? opA : (OT*)nullptr, wp);
-    GTB_LAUNCHED();
+    const float emb_scale = c.embed_scale != 0.0f ? c.embed_scale : 1.0f;
+    if (m->sandwich && c.bigram_buckets == 0) {     // embedding and the first layer's input norm in one kernel; every later norm comes out of a residual update
+        k_embed_norm<OT><<<R, 256, 0, st>>>(t, m->embed, W, emb_scale, sw_norm(m, m->L[m->runs[0].layer], 0), m->x, opA, wp);
+        GTB_LAUNCHED();
+    } else {
+        k_embed<OT><<<R, 256, 0, st>>>(t, m->embed, m->bigram, c.bigram_buckets, c.bigram_mul_prev, c.bigram_mul_cur, W, emb_scale,
+                                       m->prenorm ? m->xs : m->x, c.loop_times > 0 ? m->x0 : nullptr, first_reads_x ? opA : (OT*)nullptr, wp);
+        GTB_LAUNCHED();
+        if (m->sandwich) {
+            k_norm_rows<OT><<<R, 256, 0, st>>>(m->x, W, sw_norm(m, m->L[m->runs[0].layer], 0), nullptr, opA, wp);
+            GTB_LAUNCHED();
+        }
+    }
     bool x_in_opA = first_reads_x;
     PendingUpdate pend;                       // pre-norm layers: the embedding fills the first copy of the stream only
     for (size_t u = 0; u < m->runs.size(); u++) {
         const Run& run = m->runs[u];
         const LayerW& l = m->L[run.layer];
+        if (l.d.style == GTB_BLOCK_SANDWICH) {
+            const NormArgs next = u + 1 < m->runs.size() ? sw_norm(m, m->L[m->runs[u + 1].layer], 0) : NormArgs{};
+            int rc = run_sandwich_layer<OT>(m, t, R, S, run, l, portions, seg_lens, n_qtiles, next);
+            if (rc) return rc;
+            if (m->capture) {
+                GTB_CUDA(cudaMemcpyAsync(m->cap + u * (size_t)m->max_rows * W, m->x, (size_t)R * W * sizeof(float), cudaMemcpyDeviceToDevice, st));
+                m->cap_rows = R;
+            }
+            continue;
+        }
         if (l.d.style == GTB_BLOCK_PRENORM) {
             float* cap_prev = (m->capture && u > 0) ? m->cap + (u - 1) * (size_t)m->max_rows * W : nullptr;
             int rc = run_prenorm_layer<OT>(m, t, R, S, run, l, portions, seg_lens, seg_slots, n_qtiles, pend, cap_prev);
@@ -792,34 +1025,8 @@ int run_pass(gtb_seq_model* m, const PassTables& t, int R, int S, bool from_pend
                     GTB_LAUNCHED();
                 }
             } else {
-                const RetBranch a = ret_args(m, b);
-                const RetChunk rcfg = ret_chunk(b.d);
-                if (portions && rcfg.ok) {
-                    int n_chunks = 0;
-                    for (int s = 0; s < S; s++) n_chunks += (seg_lens[s] + rcfg.C - 1) / rcfg.C;
-                    const size_t need = (size_t)n_chunks * a.heads * a.dim * a.vdim;
-                    if (need > m->retU_floats) return gtb::fail(GTB_ERR_STATE, "chunk workspace too small (%zu > %zu floats)", need, m->retU_floats);
-                    const int nvs = (a.vdim + rcfg.vs - 1) / rcfg.vs;
-                    k_ret_rotate<<<R, 128, 0, st>>>(t, a, m->P, l.n1);
-                    GTB_LAUNCHED();
-                    if (rcfg.smem_kv > 48 * 1024) GTB_CUDA(cudaFuncSetAttribute(k_ret_chunk_kv, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)rcfg.smem_kv));
-                    k_ret_chunk_kv<<<dim3(n_chunks, a.heads, nvs), 256, rcfg.smem_kv, st>>>(t, a, m->P, l.n1, S, rcfg.C, rcfg.vs, m->retU);
-                    GTB_LAUNCHED();
-                    k_ret_scan<<<dim3(S, a.heads, (a.dim * a.vdim + 255) / 256), 256, 0, st>>>(t, a, S, rcfg.C, m->retU, run.state[bi]);
-                    GTB_LAUNCHED();
-                    if (rcfg.smem_out > 48 * 1024) GTB_CUDA(cudaFuncSetAttribute(k_ret_chunk_out, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)rcfg.smem_out));
-                    k_ret_chunk_out<<<dim3(n_chunks, a.heads, nvs), 256, rcfg.smem_out, st>>>(t, a, m->P, l.n1, S, rcfg.C, rcfg.vs, m->retU, m->O);
-                    GTB_LAUNCHED();
-                    k_ret_post<OT><<<dim3(R, (a.heads + 3) / 4), 128, 0, st>>>(a, m->O, m->P, l.n1, opC, l.kout_p);
-                    GTB_LAUNCHED();
-                    continue;
-                }
-                const RetLaunch rl = ret_launch(b.d);
-                if (rl.smem > 48 * 1024) GTB_CUDA(cudaFuncSetAttribute(k_retention, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)rl.smem));
-                k_retention<<<dim3(S, a.heads, rl.nvs), rl.block, rl.smem, st>>>(t, a, m->P, l.n1, run.state[bi], m->O, rl.vs);
-                GTB_LAUNCHED();
-                k_ret_post<OT><<<dim3(R, (a.heads + 3) / 4), 128, 0, st>>>(a, m->O, m->P, l.n1, opC, l.kout_p);
-                GTB_LAUNCHED();
+                int rc2 = run_retention<OT>(m, t, R, S, run, bi, l, portions, seg_lens);
+                if (rc2) return rc2;
             }
         }
         if (l.ff > 0 && !ff_done) {
@@ -835,7 +1042,11 @@ int run_pass(gtb_seq_model* m, const PassTables& t, int R, int S, bool from_pend
         }
     }
     if (n_want > 0) {
-        if (c.final_norm == 2) {
+        if (c.final_norm == 3) {
+            NormArgs fn{};
+            fn.kind = GTB_NORM_LAYER; fn.w = m->final_gain; fn.b = m->final_b; fn.eps = c.eps;
+            k_norm_rows<OT><<<n_want, 256, 0, st>>>(m->x, W, fn, d_want, opH, wp);
+        } else if (c.final_norm == 2) {
             NormArgs fn{};
             fn.kind = GTB_NORM_DYT; fn.w = m->final_gain; fn.b = m->final_b; fn.alpha = m->final_a;
             k_dyt_rows<OT><<<n_want, 256, 0, st>>>(m->x, W, fn, d_want, opH, wp);
@@ -893,11 +1104,15 @@ int gtb_seq_create(gtb_seq_t* out, const gtb_seq_config* cfg, const gtb_seq_laye
     }
     TRY(dalloc_t(m, &m->head, (size_t)c.vocab * wp));
     want_matrix(m, "head", m->head, c.vocab, W, wp);
-    REQ(c.final_norm >= 0 && c.final_norm <= 2);
+    REQ(c.final_norm >= 0 && c.final_norm <= 3);
     REQ(c.streams >= 0 && c.streams <= HC_MAX && c.logit_softcap >= 0.0f);
     TRY(dalloc_t(m, &m->final_gain, c.final_norm ? W : 1));
     if (c.final_norm) want_vector(m, "final.norm", m->final_gain, W, 0);
     else want_vector(m, "final.norm", m->final_gain, 0, 0, true);
+    if (c.final_norm == 3) {
+        TRY(dalloc_t(m, &m->final_b, W));
+        want_vector(m, "final.norm.b", m->final_b, W, 0);
+    }
     if (c.final_norm == 2) {
         TRY(dalloc_t(m, &m->final_b, W));
         TRY(dalloc_t(m, &m->final_a, 1));
@@ -906,6 +1121,7 @@ int gtb_seq_create(gtb_seq_t* out, const gtb_seq_config* cfg, const gtb_seq_laye
     }
     m->ns = c.streams > 0 ? c.streams : 1;
     m->prenorm = layers[0].style == GTB_BLOCK_PRENORM;
+    m->sandwich = layers[0].style == GTB_BLOCK_SANDWICH;
     if (m->prenorm && c.streams == 0) {
         TRY(dalloc_t(m, &m->hc_one, 3));
         const float one[3] = {1.0f, 1.0f, 1.0f};
@@ -922,13 +1138,15 @@ int gtb_seq_create(gtb_seq_t* out, const gtb_seq_config* cfg, const gtb_seq_laye
     for (int i = 0; i < c.n_layers; i++) {
         LayerW& l = m->L[i];
         l.d = layers[i];
-        const bool post = l.d.style == GTB_BLOCK_POSTNORM, pre = l.d.style == GTB_BLOCK_PRENORM;
-        REQ(l.d.style == GTB_BLOCK_PARALLEL || post || pre);
+        const bool post = l.d.style == GTB_BLOCK_POSTNORM, pre = l.d.style == GTB_BLOCK_PRENORM, sw = l.d.style == GTB_BLOCK_SANDWICH;
+        REQ(l.d.style == GTB_BLOCK_PARALLEL || post || pre || sw);
         REQ(pre == m->prenorm);                  // the copies of the stream belong to the whole model: pre-norm layers do not mix with the other styles
-        REQ(!pre || (c.loop_times == 0 && c.taps == 0));
+        REQ(sw == m->sandwich);                  // a sandwich layer hands its successor a normalised operand
+        REQ(!(pre || sw) || (c.loop_times == 0 && c.taps == 0));
         REQ(l.d.n_branches >= 1 && l.d.n_branches <= (post || pre ? 1 : 2));
         REQ(l.d.ff >= 0);
-        if (pre) REQ((l.d.norm_kind == GTB_NORM_RMS || l.d.norm_kind == GTB_NORM_DYT) && (l.d.ff == 0 || l.d.ff_kind == GTB_FF_GEGLU || l.d.ff_kind == GTB_FF_GATED_EXPERTS));
+        if (sw) REQ((l.d.norm_kind == GTB_NORM_RMS || l.d.norm_kind == GTB_NORM_LAYER) && (l.d.ff == 0 || l.d.ff_kind == GTB_FF_SWIGLU || l.d.ff_kind == GTB_FF_GROUP_EXPERTS));
+        else if (pre) REQ((l.d.norm_kind == GTB_NORM_RMS || l.d.norm_kind == GTB_NORM_DYT) && (l.d.ff == 0 || l.d.ff_kind == GTB_FF_GEGLU || l.d.ff_kind == GTB_FF_GATED_EXPERTS));
         else REQ(post ? (l.d.ff == 0 || l.d.ff_kind == GTB_FF_POLYNORM || l.d.ff_kind == GTB_FF_EXPERTS) : l.d.ff_kind == GTB_FF_GEGLU);
         l.ff = l.d.ff;
         const std::string lp = "l" + std::to_string(i) + ".";
@@ -937,7 +1155,8 @@ int gtb_seq_create(gtb_seq_t* out, const gtb_seq_config* cfg, const gtb_seq_laye
             BranchW& b = l.br[bi];
             b.d = l.d.branch[bi];
             gtb_seq_branch& d = b.d;
-            REQ(pre ? d.kind == GTB_MIX_LATENT_ATTN : post ? (d.kind == GTB_MIX_MINGRU || d.kind == GTB_MIX_SOFTMAX_ATTN) : (d.kind == GTB_MIX_SIGMOID_ATTN || d.kind == GTB_MIX_RETENTION));
+            REQ(pre ? d.kind == GTB_MIX_LATENT_ATTN : post ? (d.kind == GTB_MIX_MINGRU || d.kind == GTB_MIX_SOFTMAX_ATTN) :
+                sw ? (d.kind == GTB_MIX_SOFTMAX_ATTN || d.kind == GTB_MIX_RETENTION) : (d.kind == GTB_MIX_SIGMOID_ATTN || d.kind == GTB_MIX_RETENTION));
             if (d.kind == GTB_MIX_LATENT_ATTN) {
                 REQ(d.heads > 0 && d.dim > 0 && d.rope_dim >= 0 && d.vdim > 0 && d.kv_rank > 0 && d.q_rank >= 0 && d.window >= 0);
                 REQ(d.kv_rank <= 512 && d.kv_rank + d.rope_dim <= 1024);        // the absorbed form runs on the row kernels of softmax attention
@@ -977,20 +1196,28 @@ int gtb_seq_create(gtb_seq_t* out, const gtb_seq_config* cfg, const gtb_seq_laye
             if (d.kind == GTB_MIX_RETENTION) d.kv_heads = d.heads;
             REQ(d.kv_heads > 0 && d.heads % d.kv_heads == 0);
             REQ(d.rot_dims >= 0 && d.rot_dims <= d.dim && d.rot_dims % 2 == 0);
-            b.kq = d.heads * d.dim; b.kk = d.kv_heads * d.dim; b.kv = d.kv_heads * d.vdim;
+            if (d.kind != GTB_MIX_SOFTMAX_ATTN || !sw) { REQ(d.maps <= 1 && d.chunk == 0 && d.bias == 0 && d.rot_divide == 0.0f && d.qk_norm <= 2); d.maps = 1; }
+            if (d.kind != GTB_MIX_RETENTION || !sw) REQ(d.act == 0 && d.out_norm <= 1);
+            if (d.maps < 1) d.maps = 1;
+            b.kq = d.heads * d.maps * d.dim; b.kk = d.kv_heads * d.maps * d.dim; b.kv = d.kv_heads * d.vdim;
             if (d.kind == GTB_MIX_SOFTMAX_ATTN) {
-                REQ(d.qk_norm >= 0 && d.qk_norm <= 2 && d.gated >= 0 && d.gated <= 2 && d.window >= 0 && d.pool >= 0 && d.softcap >= 0.0f);
+                REQ(d.qk_norm >= 0 && d.qk_norm <= 3 && d.gated >= 0 && d.gated <= 3 && d.window >= 0 && d.pool >= 0 && d.softcap >= 0.0f);
+                REQ(d.maps <= 2 && d.chunk >= 0 && d.rot_divide >= 0.0f && (d.gated != 3 || sw));
+                if (d.maps == 2) REQ(d.pool == 0 && d.sink == 0 && (d.gated == 0 || d.gated == 3));
+                if (!sw) d.out_scale = 1.0f;
                 REQ(d.kv_from < i);
                 if (d.kv_from >= 0) {
                     REQ(c.loop_times == 0);
                     const LayerW& src = m->L[d.kv_from];
-                    REQ(src.d.style == GTB_BLOCK_POSTNORM && src.br[0].d.kind == GTB_MIX_SOFTMAX_ATTN && src.br[0].d.kv_from < 0);
-                    REQ(src.br[0].d.kv_heads == d.kv_heads && src.br[0].d.dim == d.dim && src.br[0].d.vdim == d.vdim);
+                    REQ(src.d.style == l.d.style && src.d.n_branches == 1 && src.br[0].d.kind == GTB_MIX_SOFTMAX_ATTN && src.br[0].d.kv_from < 0);
+                    REQ(src.br[0].d.kv_heads == d.kv_heads && src.br[0].d.dim == d.dim && src.br[0].d.vdim == d.vdim && src.br[0].d.maps == d.maps);
+                    REQ(l.d.n_branches == 1);
                 } else d.kv_from = -1;
                 b.q_off = n1; n1 += b.kq;
                 if (d.kv_from < 0) { b.k_off = n1; n1 += b.kk; b.v_off = n1; n1 += b.kv; }
-                if (d.gated) { b.g_off = n1; n1 += d.heads * d.vdim; }
+                if (d.gated) { b.g_off = n1; n1 += d.gated == 3 ? d.heads : d.heads * d.vdim; }
                 b.a_off = ko; ko += d.heads * d.vdim;
+                if (d.maps == 2) m->ro_max = std::max(m->ro_max, 2 * d.heads * d.vdim);
                 if (d.rot_dims > 0) {
                     // frequencies in double, rounded once: base^(-2k/dims); long wavelengths slowed down by rot_factor, a linear blend between
                     b.inv_freq.resize(d.rot_dims / 2);
@@ -1001,6 +1228,7 @@ int gtb_seq_create(gtb_seq_t* out, const gtb_seq_config* cfg, const gtb_seq_laye
                             if (wl > orig / lo) f = f / fac;
                             else if (!(wl < orig / hi)) { const double sm = (orig / wl - lo) / (hi - lo); f = (1.0 - sm) * f / fac + sm * f; }
                         }
+                        if (d.rot_divide > 0.0f) f /= (double)d.rot_divide;
                         b.inv_freq[k] = (float)f;
                     }
                     TRY(dalloc_t(m, &b.d_inv_freq, b.inv_freq.size()));
@@ -1009,6 +1237,7 @@ int gtb_seq_create(gtb_seq_t* out, const gtb_seq_config* cfg, const gtb_seq_laye
                 continue;
             }
             b.q_off = n1; b.k_off = n1 + b.kq; b.v_off = b.k_off + b.kk; n1 = b.v_off + b.kv;
+            if (d.kind == GTB_MIX_RETENTION) REQ(d.gated >= 0 && d.gated <= (sw ? 2 : 1) && d.out_norm >= 0);
             if (d.kind == GTB_MIX_RETENTION && d.gated) { b.g_off = n1; n1 += d.heads * d.vdim; }
             b.a_off = ko; ko += d.heads * d.vdim;
             if (d.kind == GTB_MIX_RETENTION) {
@@ -1029,7 +1258,7 @@ int gtb_seq_create(gtb_seq_t* out, const gtb_seq_config* cfg, const gtb_seq_laye
         }
         GTB_CUDA(cudaStreamSynchronize(ctx().stream));       // the vectors above are read from members that may move; wait for the copies
         l.n1 = n1;
-        l.kout = (post || pre) ? ko : ko + l.ff;
+        l.kout = (post || pre || sw) ? ko : ko + l.ff;
         l.kout_p = pad64(l.kout);
         TRY(dalloc_t(m, &l.w_mix, (size_t)n1 * wp));
         TRY(dalloc_t(m, &l.w_out, (size_t)W * l.kout_p));
@@ -1076,7 +1305,14 @@ int gtb_seq_create(gtb_seq_t* out, const gtb_seq_config* cfg, const gtb_seq_laye
                 want_matrix(m, bp + "k", l.w_mix + (size_t)b.k_off * wp, b.kk, W, wp);
                 want_matrix(m, bp + "v", l.w_mix + (size_t)b.v_off * wp, b.kv, W, wp);
             }
-            if ((d.kind == GTB_MIX_RETENTION || d.kind == GTB_MIX_SOFTMAX_ATTN) && d.gated) want_matrix(m, bp + "g", l.w_mix + (size_t)b.g_off * wp, d.heads * d.vdim, W, wp);
+            if (d.bias) {                           // bias vectors of the fused projection; columns without one stay zero
+                if (!l.d_bias) TRY(dalloc_t(m, &l.d_bias, n1));
+                want_vector(m, bp + "q.b", l.d_bias + b.q_off, b.kq, 0);
+                if (own_kv) { want_vector(m, bp + "k.b", l.d_bias + b.k_off, b.kk, 0); want_vector(m, bp + "v.b", l.d_bias + b.v_off, b.kv, 0); }
+            }
+            if ((d.kind == GTB_MIX_RETENTION || d.kind == GTB_MIX_SOFTMAX_ATTN) && d.gated)
+                want_matrix(m, bp + "g", l.w_mix + (size_t)b.g_off * wp, (d.kind == GTB_MIX_SOFTMAX_ATTN && d.gated == 3) ? d.heads : d.heads * d.vdim, W, wp);
+            if (d.kind == GTB_MIX_RETENTION && d.out_norm == 2) { TRY(dalloc_t(m, &b.d_onorm, d.heads * d.vdim)); want_vector(m, bp + "norm", b.d_onorm, d.heads * d.vdim, 0); }
             want_matrix(m, bp + "o", l.w_out + b.a_off, W, d.heads * d.vdim, l.kout_p);
             if (d.kind == GTB_MIX_SIGMOID_ATTN) {
                 TRY(dalloc_t(m, &b.d_pb, d.heads));
@@ -1088,10 +1324,70 @@ int gtb_seq_create(gtb_seq_t* out, const gtb_seq_config* cfg, const gtb_seq_laye
                     want_vector(m, bp + "q.norm", b.d_qnorm, d.dim, 0);
                     if (own_kv) { TRY(dalloc_t(m, &b.d_knorm, d.dim)); want_vector(m, bp + "k.norm", b.d_knorm, d.dim, 0); }
                 }
+                if (d.qk_norm == 3) {               // one weight per entry of the whole projection
+                    TRY(dalloc_t(m, &b.d_qnorm, b.kq));
+                    want_vector(m, bp + "q.norm", b.d_qnorm, b.kq, 0);
+                    if (own_kv) { TRY(dalloc_t(m, &b.d_knorm, b.kk)); want_vector(m, bp + "k.norm", b.d_knorm, b.kk, 0); }
+                    if (!m->qk_sc) TRY(dalloc_t(m, &m->qk_sc, (size_t)m->max_rows * 2));
+                }
+                if (d.maps == 2) {
+                    const char* nm[4] = {"lq1", "lk1", "lq2", "lk2"};
+                    for (int q = 0; q < 4; q++) { TRY(dalloc_t(m, &b.d_lam[q], d.dim)); want_vector(m, bp + nm[q], b.d_lam[q], d.dim, 0); }
+                }
                 if (d.sink) { TRY(dalloc_t(m, &b.d_sink, d.heads)); want_vector(m, bp + "sink", b.d_sink, d.heads, 0); }
             }
         }
-        if (pre) {
+        if (sw) {
+            const char* nn[4] = {"norm1", "norm1b", "norm2", "norm2b"};
+            for (int q = 0; q < (l.ff > 0 ? 4 : 2); q++) {
+                TRY(dalloc_t(m, &l.sn_w[q], W));
+                want_vector(m, lp + nn[q], l.sn_w[q], W, 0);
+                if (l.d.norm_kind == GTB_NORM_LAYER) { TRY(dalloc_t(m, &l.sn_b[q], W)); want_vector(m, lp + nn[q] + ".b", l.sn_b[q], W, 0); }
+            }
+            if (l.ff > 0) {
+                l.kfp = pad64(l.ff);
+                m->kfp_max = std::max(m->kfp_max, l.kfp);
+                if (l.d.ff_kind == GTB_FF_SWIGLU) {
+                    TRY(dalloc_t(m, &l.w_gu, (size_t)2 * l.ff * wp));
+                    TRY(dalloc_t(m, &l.w_down, (size_t)W * l.kfp));
+                    l.gu_inter = l.ff % 32 == 0;
+                    want_matrix(m, lp + "mlp.gate", l.w_gu, l.ff, W, wp);
+                    want_matrix(m, lp + "mlp.up", l.w_gu + (size_t)(l.gu_inter ? 32 : l.ff) * wp, l.ff, W, wp);
+                    if (l.gu_inter)
+                        for (const char* nm : {"mlp.gate", "mlp.up"}) { TensorDest& d = m->tensors[lp + nm]; d.group = 32; d.group_stride = 64; }
+                    want_matrix(m, lp + "mlp.down", l.w_down, W, l.ff, l.kfp);
+                    m->g_cols = std::max(m->g_cols, 2 * l.ff);
+                    m->kout_p_max = std::max(m->kout_p_max, l.kfp);
+                } else {
+                    const int E = l.d.experts, G = std::max(1, l.d.route_groups), keep = l.d.route_keep > 0 ? l.d.route_keep : G;
+                    REQ(E > 0 && E <= 4096 && l.d.identity == 0 && l.d.top > 0 && l.d.shared_ff >= 0 && E % G == 0 && keep <= G && l.d.top <= keep * (E / G));
+                    l.sff = l.d.shared_ff;
+                    l.n_sh = (l.sff + l.ff - 1) / l.ff;              // the shared expert in parts of one expert's inner width
+                    l.e_total = E + l.n_sh;
+                    REQ(l.d.top + l.n_sh <= 64);
+                    l.n_out = E;
+                    TRY(dalloc_t(m, &l.w_router, (size_t)E * wp));
+                    want_matrix(m, lp + "mlp.router", l.w_router, E, W, wp);
+                    TRY(dalloc_t(m, &l.w_up, (size_t)l.e_total * l.ff * wp));
+                    TRY(dalloc_t(m, &l.w_down, (size_t)l.e_total * W * l.kfp));
+                    for (int e = 0; e < E; e++) {
+                        const std::string ep = lp + "mlp.e" + std::to_string(e) + ".";
+                        want_matrix(m, ep + "up", l.w_up + (size_t)e * l.ff * wp, l.ff, W, wp);
+                        want_matrix(m, ep + "down", l.w_down + (size_t)e * W * l.kfp, W, l.ff, l.kfp);
+                    }
+                    if (l.sff > 0) {
+                        // rows of shared.up continue the stack (the last part's missing rows stay zero); columns of shared.down go part by part
+                        want_matrix(m, lp + "mlp.shared.up", l.w_up + (size_t)E * l.ff * wp, l.sff, W, wp);
+                        want_matrix(m, lp + "mlp.shared.down", l.w_down + (size_t)E * W * l.kfp, W, l.sff, l.kfp);
+                        TensorDest& d = m->tensors[lp + "mlp.shared.down"];
+                        d.split_cols = l.ff; d.split_stride = (size_t)W * l.kfp;
+                    }
+                    m->n_out_max = std::max(m->n_out_max, E);
+                    m->top_max = std::max(m->top_max, l.d.top + l.n_sh);
+                    m->e_max = std::max(m->e_max, l.e_total);
+                }
+            }
+        } else if (pre) {
             const int ns = m->ns;
             for (int q = 0; q < (l.ff > 0 ? 2 : 1); q++) {
                 const std::string np = lp + (q == 0 ? "norm1" : "norm2"), hp = lp + (q == 0 ? "hc1." : "hc2.");
@@ -1255,7 +1551,7 @@ int gtb_seq_create(gtb_seq_t* out, const gtb_seq_config* cfg, const gtb_seq_laye
                     r.kc[bi] = m->runs[d.kv_from].kc[0];
                     r.vc[bi] = m->runs[d.kv_from].vc[0];
                 } else {
-                    const size_t kb = (size_t)c.max_ctx * d.kv_heads * d.dim * es, vb = (size_t)c.max_ctx * d.kv_heads * d.vdim * es;
+                    const size_t kb = (size_t)c.max_ctx * d.kv_heads * std::max(1, d.maps) * d.dim * es, vb = (size_t)c.max_ctx * d.kv_heads * d.vdim * es;
                     TRY(dalloc(m, &r.kc[bi], kb * c.n_slots));
                     TRY(dalloc(m, &r.vc[bi], vb * c.n_slots));
                     per_slot += kb + vb;
@@ -1302,7 +1598,7 @@ int gtb_seq_create(gtb_seq_t* out, const gtb_seq_config* cfg, const gtb_seq_laye
     {
         size_t hv = 0;
         for (const LayerW& l : m->L)
-            if (l.br[0].d.kind == GTB_MIX_SOFTMAX_ATTN) hv = std::max(hv, (size_t)l.br[0].d.heads * (l.br[0].d.vdim + 2));
+            if (l.br[0].d.kind == GTB_MIX_SOFTMAX_ATTN) hv = std::max(hv, (size_t)l.br[0].d.heads * std::max(1, l.br[0].d.maps) * (l.br[0].d.vdim + 2));
             else if (l.br[0].d.kind == GTB_MIX_LATENT_ATTN) hv = std::max(hv, (size_t)l.br[0].d.heads * (l.br[0].d.kv_rank + 2));
         if (hv > 0 && c.max_ctx > 128) TRY(dalloc_t(m, &m->sattn_part, 32 * SPLIT_MAX_ROWS * hv));
     }
@@ -1394,6 +1690,10 @@ int gtb_seq_set_tensor(gtb_seq_t m, const char* name, const void* h_bf16, const 
             for (int r0 = 0; r0 < d.rows; r0 += d.group)
                 GTB_CUDA(cudaMemcpy2D((bf16*)d.dst + (size_t)(r0 / d.group) * d.group_stride * d.ld, (size_t)d.ld * 2,
                                       (const bf16*)h_bf16 + (size_t)r0 * d.cols, (size_t)d.cols * 2, (size_t)d.cols * 2, std::min(d.group, d.rows - r0), cudaMemcpyHostToDevice));
+        } else if (d.split_cols > 0) {
+            for (int c0 = 0; c0 < d.cols; c0 += d.split_cols)
+                GTB_CUDA(cudaMemcpy2D((bf16*)d.dst + (size_t)(c0 / d.split_cols) * d.split_stride, (size_t)d.ld * 2, (const bf16*)h_bf16 + c0, (size_t)d.cols * 2,
+                                      (size_t)std::min(d.split_cols, d.cols - c0) * 2, d.rows, cudaMemcpyHostToDevice));
         } else {
             GTB_CUDA(cudaMemcpy2D(d.dst, (size_t)d.ld * 2, h_bf16, (size_t)d.cols * 2, (size_t)d.cols * 2, d.rows, cudaMemcpyHostToDevice));
         }

@@ -555,12 +555,13 @@ __global__ void __launch_bounds__(256) k_moe_gu_rows(const OT* __restrict__ X, i
 }
 
 // act = row_w[r] * silu(gate) * up from G [R][2 ff] (columns laid out like the rows of the fused matrix) -> operand [R][ld_out], zero-padded
+// (grid: rows x column groups; few rows spread their columns over many CTAs)
 template <typename OT>
 __global__ void k_swiglu_rows(const float* __restrict__ G, int ff, int inter, const float* __restrict__ row_w, OT* __restrict__ out, int ld_out) {
     const int r = blockIdx.x;
     const float wt = row_w ? row_w[r] : 1.0f;
     const float* g = G + (size_t)r * 2 * ff;
-    for (int c = threadIdx.x; c < ld_out; c += blockDim.x)
+    for (int c = blockIdx.y * blockDim.x + threadIdx.x; c < ld_out; c += gridDim.y * blockDim.x)
         out[(size_t)r * ld_out + c] = cvt<OT>(c < ff ? wt * silu_(g[gu_gate_row(c, inter)]) * g[gu_up_row(c, ff, inter)] : 0.0f);
 }
 

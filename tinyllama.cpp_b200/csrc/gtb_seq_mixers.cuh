@@ -322,7 +322,8 @@ __global__ void __launch_bounds__(128) k_mingru_store(PassTables t, GruBranch b,
 struct SoftAttn {
     int heads, kv_heads, dim, vdim;
     float scale, eps, softcap;   // softcap 0: scores are not capped
-    int qk_norm;                 // 0: none, 1: unit RMS per head, 2: unit RMS times a weight vector shared by the heads
+    int qk_norm;                 // 0: none, 1: unit RMS per head, 2: unit RMS times a weight vector shared by the heads, 3: one RMS norm over the
+                                 // whole q (k) projection with a weight per entry; its scales come from qk_sc [rows][2] (k_proj_rms)
     const float *q_norm, *k_norm;
     int rot_dims, rot_layout;    // layout 0: pairs (i, i + rot_dims/2); 1: pairs (2i, 2i + 1)
     const float* inv_freq;       // [rot_dims / 2]
@@ -333,7 +334,13 @@ struct SoftAttn {
     int k_ld, v_ld;              // row strides of the key / value cache in elements; 0: packed (kv_heads * dim, kv_heads * vdim)
     int own_kv;                  // 0: keys and values are another layer's cache (nothing is projected or appended here)
     int max_ctx, max_blocks;
+    int maps;                    // 0 / 1: one score map per head; 2: two query parts per head and two key parts per K/V head ([part 1 | part 2]),
+                                 // each (head, part) an attention of its own over the head's values.  Kernels index "query units" heads * maps
+    int chunk;                   // > 0: a query sees only keys of its own chunk of positions
+    float out_scale;             // weight of the output (0 counts as 1)
+    const float* qk_sc;          // qk_norm 3
 };
+__host__ __device__ __forceinline__ int sa_maps(const SoftAttn& b) { return b.maps > 1 ? b.maps : 1; }
 
 // q (and k): per-head norm, rotary positions; q in place (fp32), k and v appended to the slot's cache.
 template <typename OT>
@@ -342,16 +349,18 @@ __global__ void __launch_bounds__(128) k_sattn_prep(PassTables t, SoftAttn b, fl
     const int slot = t.seg_slot[t.row_seg[r]], pos = t.row_pos[r];
     float* p = P + (size_t)r * ldp;
     const size_t crow = (size_t)slot * b.max_ctx + pos;
-    const int nkv = b.own_kv ? b.kv_heads : 0, half = b.rot_dims / 2;
+    const int M = sa_maps(b), nq = b.heads * M, nk = b.own_kv ? b.kv_heads * M : 0, nkv = b.own_kv ? b.kv_heads : 0, half = b.rot_dims / 2;
     const float fpos = (float)pos;
-    for (int u = blockIdx.y * nw + wid; u < b.heads + 2 * nkv; u += gridDim.y * nw) {
-        if (u < b.heads + nkv) {
-            const bool is_q = u < b.heads;
-            float* v = p + (is_q ? b.q_off + u * b.dim : b.k_off + (u - b.heads) * b.dim);
-            OT* dst = is_q ? nullptr : kc + crow * (size_t)(b.kv_heads * b.dim) + (size_t)(u - b.heads) * b.dim;
-            const float* wn = b.qk_norm == 2 ? (is_q ? b.q_norm : b.k_norm) : nullptr;
+    for (int u = blockIdx.y * nw + wid; u < nq + nk + nkv; u += gridDim.y * nw) {
+        if (u < nq + nk) {
+            const bool is_q = u < nq;
+            const int hu = is_q ? u : u - nq;
+            float* v = p + (is_q ? b.q_off : b.k_off) + hu * b.dim;
+            OT* dst = is_q ? nullptr : kc + crow * (size_t)(b.kv_heads * M * b.dim) + (size_t)hu * b.dim;
+            const float* wn = b.qk_norm == 2 ? (is_q ? b.q_norm : b.k_norm) : b.qk_norm == 3 ? (is_q ? b.q_norm : b.k_norm) + (size_t)hu * b.dim : nullptr;
             float sc = 1.0f;
-            if (b.qk_norm) {
+            if (b.qk_norm == 3) sc = b.qk_sc[(size_t)r * 2 + (is_q ? 0 : 1)];
+            else if (b.qk_norm) {
                 float ss = 0.0f;
                 for (int i = lane; i < b.dim; i += 32) ss += v[i] * v[i];
                 ss = warp_sum(ss);
@@ -370,7 +379,7 @@ __global__ void __launch_bounds__(128) k_sattn_prep(PassTables t, SoftAttn b, fl
                 if (is_q) v[i] = a; else dst[i] = cvt<OT>(a);
             }
         } else {
-            const int g = u - b.heads - nkv;
+            const int g = u - nq - nk;
             const float* v = p + b.v_off + g * b.vdim;
             OT* dst = vc + crow * (size_t)(b.kv_heads * b.vdim) + (size_t)g * b.vdim;
             for (int i = lane; i < b.vdim; i += 32) dst[i] = cvt<OT>(v[i]);
@@ -418,6 +427,7 @@ __device__ __forceinline__ float soft_cap(float s, float cap) { return cap > 0.0
 // keys a query at `pos` sees: pooled blocks 0 .. nb-1 (those that end at or before pos - window), then tokens lo .. pos
 __device__ __forceinline__ void sattn_range(const SoftAttn& b, int pos, int& lo, int& nb) {
     lo = b.window > 0 ? max(0, pos - b.window + 1) : 0;
+    if (b.chunk > 0) lo = max(lo, pos / b.chunk * b.chunk);
     nb = (b.window > 0 && b.pool > 0 && pos - b.window + 1 >= b.pool) ? (pos - b.window + 1) / b.pool : 0;
 }
 
@@ -431,13 +441,13 @@ __device__ __forceinline__ void sattn_sweep(const PassTables& t, const SoftAttn&
     float* sq = sm;                 // [dim]
     float* swt = sm + b.dim;        // [blockDim.x]
     float* red = swt + blockDim.x;  // [33]
-    const int g = h / (b.heads / b.kv_heads), slot = t.seg_slot[t.row_seg[r]];
+    const int M = sa_maps(b), g = (h / M) / (b.heads / b.kv_heads), ku = g * M + h % M, slot = t.seg_slot[t.row_seg[r]];      // h: query unit
     const float* q = P + (size_t)r * ldp + b.q_off + h * b.dim;
     for (int i = threadIdx.x; i < b.dim; i += blockDim.x) sq[i] = q[i];
-    const size_t kld = b.k_ld ? (size_t)b.k_ld : (size_t)b.kv_heads * b.dim, vld = b.v_ld ? (size_t)b.v_ld : (size_t)b.kv_heads * b.vdim;
-    const OT* kbase = kc + (size_t)slot * b.max_ctx * kld + (size_t)g * b.dim;
+    const size_t kld = b.k_ld ? (size_t)b.k_ld : (size_t)b.kv_heads * M * b.dim, vld = b.v_ld ? (size_t)b.v_ld : (size_t)b.kv_heads * b.vdim;
+    const OT* kbase = kc + (size_t)slot * b.max_ctx * kld + (size_t)ku * b.dim;
     const OT* vbase = vc + (size_t)slot * b.max_ctx * vld + (size_t)g * b.vdim;
-    const float* pkb = pk ? pk + (size_t)slot * b.max_blocks * kld + (size_t)g * b.dim : nullptr;
+    const float* pkb = pk ? pk + (size_t)slot * b.max_blocks * kld + (size_t)ku * b.dim : nullptr;
     const float* pvb = pv ? pv + (size_t)slot * b.max_blocks * vld + (size_t)g * b.vdim : nullptr;
     const bool kvec = b.dim % 8 == 0 && kld % 8 == 0;
     __syncthreads();
@@ -474,13 +484,14 @@ __device__ __forceinline__ void sattn_sweep(const PassTables& t, const SoftAttn&
 template <typename OT>
 __device__ __forceinline__ void sattn_store(const SoftAttn& b, const float* __restrict__ P, int ldp, int r, int h, float inv, const float (&acc)[4],
                                             OT* __restrict__ out, int ld_out) {
+    if (b.out_scale != 0.0f) inv *= b.out_scale;
 #pragma unroll
     for (int cc = 0; cc < 4; cc++) {
         const int c = threadIdx.x + cc * blockDim.x;
         if (c < b.vdim) {
             float o = acc[cc] * inv;
             if (b.gate) {
-                const float gt = P[(size_t)r * ldp + b.g_off + (b.gate == 3 ? h : h * b.vdim + c)];
+                const float gt = P[(size_t)r * ldp + b.g_off + (b.gate == 3 ? h / sa_maps(b) : h * b.vdim + c)];
                 o *= b.gate >= 2 ? sigmoidf_(gt) : gt * sigmoidf_(gt);
             }
             out[(size_t)r * ld_out + b.a_off + h * b.vdim + c] = cvt<OT>(o);
@@ -490,17 +501,17 @@ __device__ __forceinline__ void sattn_store(const SoftAttn& b, const float* __re
 
 // One CTA per (row, query head) over all of the row's keys.  The running maximum starts at the sink and the denominator at 1
 // (= exp(sink - sink)), so the sink counts once and no tile meets an empty history.
-template <typename OT>
+template <typename OT, typename OUT = OT>
 __global__ void __launch_bounds__(128) k_sattn(PassTables t, SoftAttn b, const float* __restrict__ P, int ldp, const OT* __restrict__ kc, const OT* __restrict__ vc,
-                                               const float* __restrict__ pk, const float* __restrict__ pv, OT* __restrict__ out, int ld_out) {
+                                               const float* __restrict__ pk, const float* __restrict__ pv, OUT* __restrict__ out, int ld_out) {
     extern __shared__ float sm[];
     const int r = blockIdx.x, h = blockIdx.y, pos = t.row_pos[r];
     int lo, nb;
     sattn_range(b, pos, lo, nb);
-    float m = b.sink ? b.sink[h] : -INFINITY, l = b.sink ? 1.0f : 0.0f;
+    float m = b.sink ? b.sink[h / sa_maps(b)] : -INFINITY, l = b.sink ? 1.0f : 0.0f;
     float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
     sattn_sweep<OT>(t, b, P, ldp, kc, vc, pk, pv, sm, r, h, 0, nb + pos - lo + 1, lo, nb, m, l, acc);
-    sattn_store<OT>(b, P, ldp, r, h, 1.0f / l, acc, out, ld_out);
+    sattn_store<OUT>(b, P, ldp, r, h, 1.0f / l, acc, out, ld_out);
 }
 
 // Decode rows: the keys of a (row, head) are split over gridDim.z CTAs in ranges of whole 128-key tiles; each leaves its running maximum,
@@ -520,7 +531,7 @@ __global__ void __launch_bounds__(128) k_sattn_split(PassTables t, SoftAttn b, c
     float m = -INFINITY, l = 0.0f;
     float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
     if (n_lo < n_hi) sattn_sweep<OT>(t, b, P, ldp, kc, vc, pk, pv, sm, r, h, n_lo, n_hi, lo, nb, m, l, acc);
-    float* o = part + (((size_t)blockIdx.z * R + r) * b.heads + h) * (b.vdim + 2);
+    float* o = part + (((size_t)blockIdx.z * R + r) * (b.heads * sa_maps(b)) + h) * (b.vdim + 2);
     if (threadIdx.x == 0) { o[0] = m; o[1] = l; }
 #pragma unroll
     for (int cc = 0; cc < 4; cc++) {
@@ -536,12 +547,12 @@ __global__ void __launch_bounds__(128) k_sattn_join(SoftAttn b, const float* __r
     __shared__ float sw[32];
     __shared__ float s_inv;
     const int r = blockIdx.x, h = blockIdx.y;
-    const size_t stride = (size_t)R * b.heads * (b.vdim + 2);
-    const float* p0 = part + ((size_t)r * b.heads + h) * (b.vdim + 2);
+    const size_t stride = (size_t)R * (b.heads * sa_maps(b)) * (b.vdim + 2);
+    const float* p0 = part + ((size_t)r * (b.heads * sa_maps(b)) + h) * (b.vdim + 2);
     if (threadIdx.x < 32) {
         const int k = threadIdx.x;
         const float mk = k < splits ? p0[k * stride] : -INFINITY, lk = k < splits ? p0[k * stride + 1] : 0.0f;
-        const float sink = b.sink ? b.sink[h] : -INFINITY;
+        const float sink = b.sink ? b.sink[h / sa_maps(b)] : -INFINITY;
         const float M = fmaxf(sink, warp_max(mk));
         const float w = mk == -INFINITY ? 0.0f : expf(mk - M);
         float l = warp_sum(lk * w);

@@ -22,7 +22,7 @@ __device__ __forceinline__ float sa_tanh(float z) {
 template <int DP, int VP>
 __global__ void __launch_bounds__(128) k_sattn_mma(PassTables t, SoftAttn b, int S, const float* __restrict__ P, int ldp, const bf16* __restrict__ kc,
                                                    const bf16* __restrict__ vc, const float* __restrict__ pk, const float* __restrict__ pv,
-                                                   bf16* __restrict__ out, int ld_out) {
+                                                   bf16* __restrict__ out, int ld_out, float* __restrict__ out_f, int ld_f) {
     constexpr int LQ = DP + 8, LV = VP + 8;
     extern __shared__ __align__(16) unsigned char sa_raw[];
     bf16* sq = reinterpret_cast<bf16*>(sa_raw);          // [64][LQ]
@@ -30,7 +30,7 @@ __global__ void __launch_bounds__(128) k_sattn_mma(PassTables t, SoftAttn b, int
     bf16* sv0 = sk0 + 2 * 64 * LQ;                      // [2][64][LV]
     int seg, q0;
     if (!sa_find_tile(t, S, blockIdx.x, seg, q0)) return;
-    const int h = blockIdx.y, g = h / (b.heads / b.kv_heads);
+    const int M = sa_maps(b), h = blockIdx.y, hd = h / M, g = hd / (b.heads / b.kv_heads), ku = g * M + h % M;     // h: query unit
     const int slot = t.seg_slot[seg], row0 = t.seg_row0[seg] + q0, nq = min(64, t.seg_len[seg] - q0);
     const int pos0 = t.row_pos[row0];                    // position of the tile's first row; row i sits at pos0 + i
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, gq = lane >> 2, tq = lane & 3;
@@ -38,16 +38,16 @@ __global__ void __launch_bounds__(128) k_sattn_mma(PassTables t, SoftAttn b, int
         const int r = e / DP, i = e % DP;
         sq[r * LQ + i] = __float2bfloat16_rn((r < nq && i < b.dim) ? P[(size_t)(row0 + r) * ldp + b.q_off + h * b.dim + i] : 0.0f);
     }
-    const size_t kld = (size_t)b.kv_heads * b.dim, vld = (size_t)b.kv_heads * b.vdim;
-    const bf16* kbase = kc + (size_t)slot * b.max_ctx * kld + (size_t)g * b.dim;
+    const size_t kld = (size_t)b.kv_heads * M * b.dim, vld = (size_t)b.kv_heads * b.vdim;
+    const bf16* kbase = kc + (size_t)slot * b.max_ctx * kld + (size_t)ku * b.dim;
     const bf16* vbase = vc + (size_t)slot * b.max_ctx * vld + (size_t)g * b.vdim;
-    const float* pkb = pk ? pk + (size_t)slot * b.max_blocks * kld + (size_t)g * b.dim : nullptr;
+    const float* pkb = pk ? pk + (size_t)slot * b.max_blocks * kld + (size_t)ku * b.dim : nullptr;
     const float* pvb = pv ? pv + (size_t)slot * b.max_blocks * vld + (size_t)g * b.vdim : nullptr;
     const bool vec = (b.dim % 8 == 0) && (b.vdim % 8 == 0);
     const int last = pos0 + nq - 1;                      // last position of the tile
     int t_lo, nb_tile;
     sattn_range(b, last, t_lo, nb_tile);                 // blocks the last row sees: the most of any row
-    t_lo = b.window > 0 ? max(0, pos0 - b.window + 1) : 0;
+    { int nb0; sattn_range(b, pos0, t_lo, nb0); }     // the first row's first token: the lowest of any row
     const int n_bt = (nb_tile + 63) / 64, n_it = n_bt + (last - t_lo) / 64 + 1;
     const uint32_t sq_a = (uint32_t)__cvta_generic_to_shared(sq);
     auto load_tile = [&](int st, int it) {
@@ -96,9 +96,10 @@ __global__ void __launch_bounds__(128) k_sattn_mma(PassTables t, SoftAttn b, int
     sattn_range(b, p_lo, tl_lo, nb_lo);
     sattn_range(b, p_hi, tl_hi, nb_hi);
     const int pw0 = pos0 + warp * 16, pw1 = pw0 + 15;      // the warp's rows
-    int wl_dummy, nb_w;
+    int wl_dummy, nb_w, wl0, nb_w0;
     sattn_range(b, pw1, wl_dummy, nb_w);
-    const float sink = b.sink ? b.sink[h] : -INFINITY;
+    sattn_range(b, pw0, wl0, nb_w0);                      // first token the warp's first row sees: no row of the warp sees an earlier one
+    const float sink = b.sink ? b.sink[hd] : -INFINITY;
     float m_lo = sink, m_hi = sink, l_lo = 0.0f, l_hi = 0.0f;
     float o[VP / 8][4];
 #pragma unroll
@@ -114,7 +115,7 @@ __global__ void __launch_bounds__(128) k_sattn_mma(PassTables t, SoftAttn b, int
         __syncthreads();
         const bool is_blk = it < n_bt;
         const int k0 = is_blk ? it * 64 : t_lo + (it - n_bt) * 64;
-        const bool skip = is_blk ? (k0 >= nb_w) : (k0 > pw1 || (b.window > 0 && k0 + 63 < pw0 - b.window + 1));
+        const bool skip = is_blk ? (k0 >= nb_w) : (k0 > pw1 || k0 + 63 < wl0);
         if (skip) { __syncthreads(); continue; }        // no row of this warp sees a key of the tile
         const uint32_t sk_a = (uint32_t)__cvta_generic_to_shared(sk0 + st * 64 * LQ), sv_a = (uint32_t)__cvta_generic_to_shared(sv0 + st * 64 * LV);
         float sc[8][4];
@@ -183,6 +184,20 @@ __global__ void __launch_bounds__(128) k_sattn_mma(PassTables t, SoftAttn b, int
     if (b.sink) { l_lo += __expf(sink - m_lo); l_hi += __expf(sink - m_hi); }
     const float i_lo = 1.0f / l_lo, i_hi = 1.0f / l_hi;
     const int r_lo = warp * 16 + gq, r_hi = r_lo + 8;
+    if (out_f) {                                         // fp32, no gate and no weight: a later kernel combines the query units
+#pragma unroll
+        for (int n = 0; n < VP / 8; n++) {
+            const int c = n * 8 + tq * 2;
+#pragma unroll
+            for (int x = 0; x < 2; x++) {
+                if (c + x >= b.vdim) continue;
+                if (r_lo < nq) out_f[(size_t)(row0 + r_lo) * ld_f + h * b.vdim + c + x] = o[n][x] * i_lo;
+                if (r_hi < nq) out_f[(size_t)(row0 + r_hi) * ld_f + h * b.vdim + c + x] = o[n][2 + x] * i_hi;
+            }
+        }
+        return;
+    }
+    const float os = b.out_scale != 0.0f ? b.out_scale : 1.0f;
 #pragma unroll
     for (int n = 0; n < VP / 8; n++) {
         const int c = n * 8 + tq * 2;
@@ -190,13 +205,13 @@ __global__ void __launch_bounds__(128) k_sattn_mma(PassTables t, SoftAttn b, int
         for (int x = 0; x < 2; x++) {
             if (c + x >= b.vdim) continue;
             if (r_lo < nq) {
-                float v = o[n][x] * i_lo;
-                if (b.gate) { const float gt = P[(size_t)(row0 + r_lo) * ldp + b.g_off + (b.gate == 3 ? h : h * b.vdim + c + x)]; v *= b.gate >= 2 ? sigmoidf_(gt) : gt * sigmoidf_(gt); }
+                float v = o[n][x] * i_lo * os;
+                if (b.gate) { const float gt = P[(size_t)(row0 + r_lo) * ldp + b.g_off + (b.gate == 3 ? hd : h * b.vdim + c + x)]; v *= b.gate >= 2 ? sigmoidf_(gt) : gt * sigmoidf_(gt); }
                 out[(size_t)(row0 + r_lo) * ld_out + b.a_off + h * b.vdim + c + x] = __float2bfloat16_rn(v);
             }
             if (r_hi < nq) {
-                float v = o[n][2 + x] * i_hi;
-                if (b.gate) { const float gt = P[(size_t)(row0 + r_hi) * ldp + b.g_off + (b.gate == 3 ? h : h * b.vdim + c + x)]; v *= b.gate >= 2 ? sigmoidf_(gt) : gt * sigmoidf_(gt); }
+                float v = o[n][2 + x] * i_hi * os;
+                if (b.gate) { const float gt = P[(size_t)(row0 + r_hi) * ldp + b.g_off + (b.gate == 3 ? hd : h * b.vdim + c + x)]; v *= b.gate >= 2 ? sigmoidf_(gt) : gt * sigmoidf_(gt); }
                 out[(size_t)(row0 + r_hi) * ld_out + b.a_off + h * b.vdim + c + x] = __float2bfloat16_rn(v);
             }
         }

@@ -50,8 +50,13 @@ def _open_nanotar(path: Path, dtype: str, n_slots: int, max_ctx: int, **kw):
     return _open_described(nanotar, path, dtype, n_slots, max_ctx, **kw)
 
 
-FAMILIES = {"Nanotar": _open_nanotar, "Reninex": _open_reninex, "Robopel": _open_robopel, "TinyLlama": _open_tinyllama}
-STEPWISE = {"Nanotar", "Reninex", "Robopel"}          # families of the layer-list library: slots, portion-wise step function, scheduler
+def _open_vulosun(path: Path, dtype: str, n_slots: int, max_ctx: int, **kw):
+    from . import vulosun
+    return _open_described(vulosun, path, dtype, n_slots, max_ctx, **kw)
+
+
+FAMILIES = {"Nanotar": _open_nanotar, "Reninex": _open_reninex, "Robopel": _open_robopel, "TinyLlama": _open_tinyllama, "Vulosun": _open_vulosun}
+STEPWISE = {"Nanotar", "Reninex", "Robopel", "Vulosun"}          # families of the layer-list library: slots, portion-wise step function, scheduler
 
 
 def family_of(path) -> str:

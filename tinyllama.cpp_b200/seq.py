@@ -13,9 +13,9 @@ LIB_PATH = HERE / "libgten_b200_seq.so"
 
 BF16, F32 = 0, 1
 MIX_SIGMOID_ATTN, MIX_RETENTION, MIX_MINGRU, MIX_SOFTMAX_ATTN, MIX_LATENT_ATTN = 1, 2, 3, 4, 5
-BLOCK_PARALLEL, BLOCK_POSTNORM, BLOCK_PRENORM = 0, 1, 2
-FF_GEGLU, FF_POLYNORM, FF_EXPERTS, FF_GATED_EXPERTS = 0, 1, 2, 3
-NORM_RMS, NORM_DYT = 0, 1
+BLOCK_PARALLEL, BLOCK_POSTNORM, BLOCK_PRENORM, BLOCK_SANDWICH = 0, 1, 2, 3
+FF_GEGLU, FF_POLYNORM, FF_EXPERTS, FF_GATED_EXPERTS, FF_SWIGLU, FF_GROUP_EXPERTS = 0, 1, 2, 3, 4, 5
+NORM_RMS, NORM_DYT, NORM_LAYER = 0, 1, 2
 ROT_HALVES, ROT_INTERLEAVED = 0, 1
 MODE_BY_NAME = {"bfloat16": BF16, "bf16": BF16, "float32": F32, "fp32": F32}
 
@@ -30,12 +30,14 @@ class BranchC(C.Structure):
                 ("gated", C.c_int), ("out_scale", C.c_float), ("decay", C.POINTER(C.c_float)), ("rot_layout", C.c_int),
                 ("rot_factor", C.c_float), ("rot_low", C.c_float), ("rot_high", C.c_float), ("rot_original", C.c_float), ("softcap", C.c_float),
                 ("window", C.c_int), ("pool", C.c_int), ("sink", C.c_int), ("kv_from", C.c_int),
-                ("rope_dim", C.c_int), ("kv_rank", C.c_int), ("q_rank", C.c_int)]
+                ("rope_dim", C.c_int), ("kv_rank", C.c_int), ("q_rank", C.c_int),
+                ("chunk", C.c_int), ("maps", C.c_int), ("diff", C.c_float), ("bias", C.c_int), ("act", C.c_int), ("rot_divide", C.c_float)]
 
 
 class LayerC(C.Structure):
     _fields_ = [("n_branches", C.c_int), ("branch", BranchC * 2), ("ff", C.c_int), ("style", C.c_int), ("ff_kind", C.c_int),
-                ("experts", C.c_int), ("top", C.c_int), ("identity", C.c_int), ("norm_kind", C.c_int), ("shared_ff", C.c_int)]
+                ("experts", C.c_int), ("top", C.c_int), ("identity", C.c_int), ("norm_kind", C.c_int), ("shared_ff", C.c_int),
+                ("route_groups", C.c_int), ("route_keep", C.c_int), ("route_scale", C.c_float)]
 
 
 class ConfigC(C.Structure):
@@ -125,7 +127,8 @@ class SeqModel:
     """A described model resident on the GPU: weights, n_slots sequences of state, the step function."""
 
     def __init__(self, desc: dict, mode: int, n_slots: int, max_ctx: int, max_rows: int = 0):
-        """desc: the flat description a model family's config reader produces (see reninex.describe, robopel.describe, nanotar.describe)."""
+        """desc: the flat description a model family's config reader produces (see reninex.describe, robopel.describe, nanotar.describe,
+        vulosun.describe)."""
         self.desc, self.mode, self.n_slots, self.max_ctx = desc, mode, n_slots, max_ctx
         self.vocab, self.width = desc["vocab"], desc["width"]
         layers = (LayerC * len(desc["layers"]))()
@@ -136,6 +139,7 @@ class SeqModel:
             lc.style, lc.ff_kind = l.get("style", BLOCK_PARALLEL), l.get("ff_kind", FF_GEGLU)
             lc.experts, lc.top, lc.identity = l.get("experts", 0), l.get("top", 0), l.get("identity", 0)
             lc.norm_kind, lc.shared_ff = l.get("norm_kind", NORM_RMS), l.get("shared_ff", 0)
+            lc.route_groups, lc.route_keep, lc.route_scale = l.get("route_groups", 0), l.get("route_keep", 0), l.get("route_scale", 1.0)
             for bc, b in zip(lc.branch, l["branches"]):
                 bc.kind, bc.name = b["kind"], b["name"].encode()
                 bc.heads, bc.kv_heads, bc.dim, bc.vdim = b["heads"], b.get("kv_heads", b["heads"]), b["dim"], b["vdim"]
@@ -147,6 +151,8 @@ class SeqModel:
                 bc.softcap, bc.window, bc.pool = b.get("softcap", 0.0), b.get("window", 0), b.get("pool", 0)
                 bc.sink, bc.kv_from = int(b.get("sink", 0)), b.get("kv_from", -1)
                 bc.rope_dim, bc.kv_rank, bc.q_rank = b.get("rope_dim", 0), b.get("kv_rank", 0), b.get("q_rank", 0)
+                bc.chunk, bc.maps, bc.diff = b.get("chunk", 0), b.get("maps", 1), b.get("diff", 0.0)
+                bc.bias, bc.act, bc.rot_divide = int(b.get("bias", 0)), int(b.get("act", 0)), b.get("rot_divide", 0.0)
                 if b.get("decay") is not None:
                     arr = (C.c_float * len(b["decay"]))(*b["decay"])
                     self._keep.append(arr)
