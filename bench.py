@@ -1,7 +1,7 @@
 #!/usr/bin/env python
 """bench.py -- batch-1 greedy decode throughput of the tinyllama.cpp forward hot path on B200.
 
-  python bench.py [--gpus N] [--steps K] [--warmup W] [--workload q4|q8|f16|prefill_q8|q4_seq64|reninex|robopel|nanotar] [--impl b200|reference]
+  python bench.py [--gpus N] [--steps K] [--warmup W] [--workload q4|q8|f16|prefill_q8|q4_seq64|reninex|robopel|nanotar|vulosun] [--impl b200|reference]
 
 One "step" = one decoded token = one pass of the hot path (TinyLlama::logits for one new row + argmax).
 Default workload = BASELINE.json configs[2], the configuration north_star's target is quoted on:
@@ -566,7 +566,7 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=512)
     ap.add_argument("--warmup", type=int, default=16)
-    ap.add_argument("--workload", choices=list(WORKLOADS) + ["prefill_q8", "q4_seq64", "reninex", "robopel", "nanotar"], default="q4")
+    ap.add_argument("--workload", choices=list(WORKLOADS) + ["prefill_q8", "q4_seq64", "reninex", "robopel", "nanotar", "vulosun"], default="q4")
     ap.add_argument("--impl", choices=["b200", "reference"], default="b200")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
@@ -594,6 +594,11 @@ def main():
             return
         from tinyllama_cpp_b200 import bench_seq
         return bench_seq.run_nanotar(args, ROOT, ClockSampler)
+    if args.workload == "vulosun":        # the Vulosun family beside Robopel at the same width and layer count (N = 1)
+        if int(os.environ.get("RANK", "0")) != 0:
+            return
+        from tinyllama_cpp_b200 import bench_seq
+        return bench_seq.run_vulosun(args, ROOT, ClockSampler)
     wdt, cfg_idx, desc = WORKLOADS[args.workload]
     if args.impl == "reference":
         return run_reference(args, wdt, desc)

@@ -2,7 +2,9 @@
 (random weights), beside TinyLlama at the same layer shape and layer count.  `bench.py --workload robopel`: the same for the Robopel
 family, beside Reninex (the closest existing model: same library, same width and layer count).  `bench.py --workload nanotar`: the Nanotar
 family beside Robopel (the closest existing model: softmax attention with a window, a sink and an output gate, routed experts) at the same
-widths and layer count.  Timed with CUDA events on each library's own stream,
+widths and layer count.  `bench.py --workload vulosun`: the Vulosun family beside Robopel (the closest existing model: sequential sublayers
+with norms on their outputs, softmax attention with a sink, a gate and a shared cache, squared-ReLU experts) at the same widths and layer
+count.  Timed with CUDA events on each library's own stream,
 after warm-up; the weights of one pass (hundreds of MB) are larger than L2, so every pass streams them from HBM."""
 from __future__ import annotations
 
@@ -342,6 +344,152 @@ def nanotar_section(torch, name, T, iters, warmup, peaks):
     out["state_bytes_per_slot_at_T"] = state_bytes
     m.close()
     return out
+
+
+VULOSUN_SIZES = {
+    # width, dense ff; gated attention heads / kv x dim | vdim; differential heads / kv x (2 x dim) | vdim and its chunk; parallel: left heads / kv x dim | vdim,
+    # right heads x dim | vdim; experts x ff (top, groups, kept) + shared ff
+    "w2048": dict(width=2048, ff=5632, heads=32, kv=4, dim=64, vdim=64, d_heads=16, d_kv=4, d_dim=64, d_vdim=128, chunk=1024, l_heads=16, l_kv=4, l_dim=64, l_vdim=64,
+                  r_heads=8, r_dim=128, r_vdim=128, experts=16, top=2, groups=4, keep=2, eff=1408, sff=1408),
+    "w1024": dict(width=1024, ff=2816, heads=16, kv=4, dim=64, vdim=64, d_heads=8, d_kv=4, d_dim=64, d_vdim=128, chunk=512, l_heads=8, l_kv=4, l_dim=64, l_vdim=64,
+                  r_heads=4, r_dim=128, r_vdim=128, experts=16, top=2, groups=4, keep=2, eff=704, sff=704),
+}
+
+
+def vulosun_config(name, vocab=32000):
+    """Four layers: differential attention + dense, parallel (sink attention | decayed recurrence) + experts, gated attention + experts,
+    differential attention on layer 0's cache + dense."""
+    from . import vulosun as VU
+    z = VULOSUN_SIZES[name]
+    dif = dict(heads=z["d_heads"], kv_heads=z["d_kv"], dim=z["d_dim"], vdim=z["d_vdim"], diff=0.5, chunk=z["chunk"], rot_dims=32, rot_base=10000.0, factor=8.0)
+    moe = lambda: VU.moe_mlp(experts=z["experts"], top=z["top"], ff=z["eff"], groups=z["groups"], keep=z["keep"], scale=2.0, shared_ff=z["sff"])
+    layers = [VU.differential_layer(mlp=VU.dense_mlp(z["ff"]), **dif),
+              VU.parallel_layer(heads=z["l_heads"], kv_heads=z["l_kv"], dim=z["l_dim"], vdim=z["l_vdim"], rot_dims=32, rot_base=100000.0, r_heads=z["r_heads"], r_dim=z["r_dim"],
+                                r_vdim=z["r_vdim"], decay=[float(1.0 - 2.0 ** (-3 - h)) for h in range(z["r_heads"])], left_scale=1.0, right_scale=0.8, mlp=moe()),
+              VU.gated_attention_layer(heads=z["heads"], kv_heads=z["kv"], dim=z["dim"], vdim=z["vdim"], rot_dims=z["dim"], rot_base=250000.0, mlp=moe()),
+              VU.differential_layer(kv_from=0, mlp=VU.dense_mlp(z["ff"]), **dif)]
+    return VU.make_config(vocab=vocab, width=z["width"], layers=layers, eps=1e-6)
+
+
+def vulosun_counts(desc, T):
+    """(weights every token multiplies, FLOPs of the mixers' own arithmetic for a T-token prompt, bytes of weights a decode step of one
+    sequence reads) -- routed experts count `top` experts per token, attention the keys a row really sees."""
+    from .seq import FF_GROUP_EXPERTS, MIX_RETENTION
+    W, params, mix = desc["width"], 0, 0.0
+    for l in desc["layers"]:
+        per = 0
+        for b in l["branches"]:
+            H, D, V = b["heads"], b["dim"], b["vdim"]
+            if b["kind"] == MIX_RETENTION:
+                per += W * (2 * H * D + 3 * H * V)
+                mix += 4.0 * H * D * V * T                        # state update and read per token
+                continue
+            M, G = b.get("maps", 1), b["kv_heads"]
+            per += W * (H * M * D + H * V) + (W * G * (M * D + V) if b.get("kv_from", -1) < 0 else 0) + (W * H if b.get("gated") == 3 else 0)
+            ch = b.get("chunk", 0)
+            keys = sum(i % ch + 1 for i in range(T)) if ch else T * (T + 1) / 2
+            mix += 2.0 * H * M * (D + V) * keys
+        if l["ff"]:
+            per += (W * l["experts"] + l["top"] * 2 * W * l["ff"] + 2 * W * l.get("shared_ff", 0)) if l.get("ff_kind") == FF_GROUP_EXPERTS else 3 * W * l["ff"]
+        params += per
+    return params + desc["vocab"] * W, mix, 2 * (params + desc["vocab"] * W)
+
+
+def vulosun_section(torch, name, T, iters, warmup, peaks):
+    from . import vulosun as VU, seq
+    cfg = vulosun_config(name)
+    desc = VU.describe(cfg)
+    t0 = time.time()
+    rng = np.random.default_rng(0)
+    tensors = {}
+    for k, shape in VU.tensor_shapes(desc).items():              # cheap random bf16 patterns of the right scale
+        n = int(np.prod(shape))
+        leaf = k.split(".")[-1]
+        if leaf == "b":
+            a = np.zeros(n, np.uint16)
+        elif leaf.startswith("norm"):
+            a = np.full(n, 0x3F80, np.uint16)
+        else:
+            std = 1.0 if k == "embed" or leaf == "sink" else (0.1 if leaf in ("lq1", "lk1", "lq2", "lk2") else 1.0 / np.sqrt(shape[-1]))
+            a = VU.st.f32_to_bf16_bits(rng.standard_normal(n, np.float32) * np.float32(std))
+        tensors[k] = a.reshape(shape)
+    n_slots = 8
+    m = seq.SeqModel(desc, seq.BF16, n_slots, T + 64, max_rows=T).load(tensors)
+    stream = torch.cuda.ExternalStream(seq.stream_handle(), device=torch.device("cuda", 0))
+    prompt = rng.integers(0, desc["vocab"], T).astype(np.int32)
+    params, mix, dec_bytes = vulosun_counts(desc, T)
+    out = {"size": name, "layers": len(desc["layers"]), "params_matmul_per_token": params, "weight_bytes": m.weight_bytes(), "setup_s": round(time.time() - t0, 1)}
+
+    def prefill():
+        m.reset(0)
+        m.step([(0, prompt)], [T - 1])
+    l0 = seq.launch_count()
+    prefill()
+    out["prefill_launches"] = seq.launch_count() - l0
+    ms = _events(torch, stream, prefill, iters, warmup)
+    flops = 2.0 * T * params - 2.0 * (T - 1) * desc["vocab"] * desc["width"] + mix
+    out["prefill"] = {"T": T, "ms": ms, "tokens_per_s": T / ms * 1e3, "tflops": flops / ms * 1e-9, "frac_of_bf16_peak": flops / ms * 1e-9 / peaks["tflops"],
+                      "note": "includes the host->device copy of the prompt and the device->host copy of the last row's logits; experts count top per token"}
+
+    def chunked():                                                # the same prompt in four portions
+        m.reset(0)
+        for i in range(0, T, T // 4):
+            m.step([(0, prompt[i:i + T // 4])], [T // 4 - 1])
+    out["prefill_in_4_portions_ms"] = _events(torch, stream, chunked, max(3, iters // 2), 2)
+    for s in range(n_slots):
+        m.reset(s)
+        m.step_greedy([(s, prompt[: T - 40])])
+    state_bytes = m.state_bytes_per_slot() * (T - 40) / (T + 64)
+    for nseq in (1, 8):
+        slots, steps = list(range(nseq)), 8
+        m.decode(slots, 2)
+        l0 = seq.launch_count()
+        t_ms = []
+        with torch.cuda.stream(stream):
+            for _ in range(3):
+                a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+                a.record(stream)
+                m.decode(slots, steps)
+                b.record(stream)
+                torch.cuda.synchronize()
+                t_ms.append(a.elapsed_time(b) / steps)
+        ms = float(np.median(t_ms))
+        by = dec_bytes
+        out[f"decode_{nseq}"] = {"ms_per_step": ms, "tokens_per_s": nseq / ms * 1e3, "bytes_per_step_one_sequence": by, "gbs": by / ms * 1e-6,
+                                 "frac_of_hbm_peak": by / ms * 1e-6 / peaks["hbm_gbs"],
+                                 "note": "bytes: weights one sequence's step reads (top experts per routed layer); further sequences add their experts, keys and state"}
+    out["state_bytes_per_slot_at_T"] = state_bytes
+    m.close()
+    return out
+
+
+def run_vulosun(args, root, clock_sampler) -> None:
+    """`--workload vulosun`: Vulosun at two sizes, Robopel at the same widths and layer count in the same call."""
+    import torch
+    from . import build, seq
+    build.build(target="seq")
+    torch.cuda.set_device(0)
+    peaks = _peaks(root)
+    seq.init(0)
+    T = 2048
+    iters = max(3, min(args.steps if args.steps != 512 else 5, 20))
+    warm = max(args.warmup if args.warmup != 16 else 3, 3)
+    res = {"vulosun": [], "robopel_same_width": [], "peaks": peaks}
+    only = getattr(args, "sizes", None)
+    with clock_sampler(0) as clk:
+        for name in VULOSUN_SIZES:
+            if not only or name in only:
+                res["vulosun"].append(vulosun_section(torch, name, T, iters, warm, peaks))
+        for name in ROBOPEL_SIZES:
+            if not only or name in only:
+                res["robopel_same_width"].append(robopel_section(torch, name, T, iters, warm, peaks))
+    head = res["vulosun"][0]
+    print(json.dumps({"metric": "vulosun_prefill_tokens_per_s", "value": head["prefill"]["tokens_per_s"], "unit": "tokens/s", "n_gpus": 1,
+                      "steps": iters, "warmup": warm, "ms_per_step": head["prefill"]["ms"], "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+                      "dtype": "bf16 operands, fp32 accumulation; fp32 stream, norms, scores, recurrent state, router", "data": "synthetic",
+                      "config": {"workload": f"Vulosun {head['size']} x {head['layers']} layers, random weights: prefill of {T} tokens; decode at that context",
+                                 "l2": "weights of a pass exceed L2"},
+                      "detail": res, "gpu_launches": head["prefill_launches"], "clocks": clk.summary()}), flush=True)
 
 
 def _peaks(root):
