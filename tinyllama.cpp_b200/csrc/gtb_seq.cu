@@ -518,6 +518,16 @@ NormArgs sw_norm(const gtb_seq_model* m, const LayerW& l, int q) {          // q
     return n;
 }
 
+// the residual update with the fewest kept values per thread that hold a row of this width
+template <typename OT>
+void sandwich_add(int R, size_t smem, const float* Y, const float* Y2, const float* Yg, const int* pair_dst, int top, int W, const NormArgs& post, float* x, const NormArgs& next,
+                  OT* op, int ld_op, const GroupRouteNext& rn) {
+    cudaStream_t st = ctx().stream;
+    if (W <= 1024) k_sandwich_add<OT, 1><<<R, 256, smem, st>>>(Y, Y2, Yg, pair_dst, top, W, post, x, next, op, ld_op, rn);
+    else if (W <= 2048) k_sandwich_add<OT, 2><<<R, 256, smem, st>>>(Y, Y2, Yg, pair_dst, top, W, post, x, next, op, ld_op, rn);
+    else k_sandwich_add<OT, 4><<<R, 256, smem, st>>>(Y, Y2, Yg, pair_dst, top, W, post, x, next, op, ld_op, rn);
+}
+
 // One softmax-attention branch of a sandwich layer on R rows: projections in m->P, output into the out-projection operand.
 template <typename OT>
 int run_soft_branch(gtb_seq_model* m, const PassTables& t, int R, int S, const Run& run, int bi, const LayerW& l, bool portions, int n_qtiles) {
@@ -601,7 +611,7 @@ int run_sandwich_layer(gtb_seq_model* m, const PassTables& t, int R, int S, cons
         rn.w = l.w_router; rn.ldw = wp; rn.n_exp = l.d.experts; rn.n_groups = groups; rn.keep = keep; rn.top = l.d.top; rn.n_always = l.n_sh; rn.scale = l.d.route_scale;
         rn.sel_idx = m->sel_idx; rn.sel_w = m->sel_w;
     }
-    k_sandwich_add<OT><<<R, 256, rn.w ? rn_smem : 0, st>>>(m->Y, nullptr, nullptr, nullptr, 0, W, sw_norm(m, l, 1), m->x, l.ff > 0 ? sw_norm(m, l, 2) : next, opA, wp, rn);
+    sandwich_add<OT>(R, rn.w ? rn_smem : 0, m->Y, nullptr, nullptr, nullptr, 0, W, sw_norm(m, l, 1), m->x, l.ff > 0 ? sw_norm(m, l, 2) : next, opA, wp, rn);
     GTB_LAUNCHED();
     if (l.ff == 0) return GTB_OK;
     if (l.d.ff_kind == GTB_FF_SWIGLU) {
@@ -619,7 +629,7 @@ int run_sandwich_layer(gtb_seq_model* m, const PassTables& t, int R, int S, cons
         }
         rc = product<OT>(m, opC, l.kfp, l.w_down, l.kfp, m->Y, W, R, W, l.kfp, nullptr, 0);
         if (rc) return rc;
-        k_sandwich_add<OT><<<R, 256, 0, st>>>(m->Y, nullptr, nullptr, nullptr, 0, W, sw_norm(m, l, 3), m->x, next, opA, wp, GroupRouteNext{});
+        sandwich_add<OT>(R, 0, m->Y, nullptr, nullptr, nullptr, 0, W, sw_norm(m, l, 3), m->x, next, opA, wp, GroupRouteNext{});
         GTB_LAUNCHED();
         return GTB_OK;
     }
@@ -641,7 +651,7 @@ int run_sandwich_layer(gtb_seq_model* m, const PassTables& t, int R, int S, cons
         if (rc == 0) rc = seq_gemm_bf16_grouped(m->gp, m->actg, l.kfp, l.w_down, l.kfp, mpad, W, l.kfp, Et, m->tile_e, m->Yg, W, nullptr, 0, nullptr);
         if (rc > 0) return rc;
         if (rc == 0) {
-            k_sandwich_add<OT><<<R, 256, 0, st>>>(nullptr, nullptr, m->Yg, m->pair_dst, top, W, sw_norm(m, l, 3), m->x, next, opA, wp, GroupRouteNext{});
+            sandwich_add<OT>(R, 0, nullptr, nullptr, m->Yg, m->pair_dst, top, W, sw_norm(m, l, 3), m->x, next, opA, wp, GroupRouteNext{});
             GTB_LAUNCHED();
             return GTB_OK;
         }
@@ -651,7 +661,7 @@ int run_sandwich_layer(gtb_seq_model* m, const PassTables& t, int R, int S, cons
     GTB_LAUNCHED();
     k_moe_down_rows<OT><<<dim3(R, std::max(1, std::min(std::max(1, 4096 / R), (W + 7) / 8))), 256, 0, st>>>((const OT*)m->act, l.kfp, l.w_down, W, Et, top, m->sel_idx, m->Y, W);
     GTB_LAUNCHED();
-    k_sandwich_add<OT><<<R, 256, 0, st>>>(m->Y, nullptr, nullptr, nullptr, 0, W, sw_norm(m, l, 3), m->x, next, opA, wp, GroupRouteNext{});
+    sandwich_add<OT>(R, 0, m->Y, nullptr, nullptr, nullptr, 0, W, sw_norm(m, l, 3), m->x, next, opA, wp, GroupRouteNext{});
     GTB_LAUNCHED();
     return GTB_OK;
 }

@@ -17,8 +17,20 @@ namespace seq {
 
 constexpr int SW_NORM_LAYER = 2;            // NormArgs::kind of a layer norm (GTB_NORM_LAYER); anything else here: RMS with a plain weight
 
+// Sum over the block with ONE barrier: every warp leaves its partial sum in `slot` (32 floats that no other reduction of the kernel uses, so
+// nothing has to wait for earlier readers) and every thread adds the partial sums itself, in the same order.
+__device__ __forceinline__ float sw_block_sum(float v, float* slot) {
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5, nw = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    if (lane == 0) slot[wid] = v;
+    __syncthreads();
+    float t = 0.0f;
+    for (int w = 0; w < nw; w++) t += slot[w];
+    return t;
+}
 // mean and 1 / sqrt(variance + eps) of a row (layer norm), or 0 and 1 / sqrt(mean square + eps) (RMS); a thread holds the values of columns
-// (threadIdx.x + i blockDim.x) * 4 .. + 3 in v[4 i ..].  The mean first, then the squared deviations: no cancellation between two large sums
+// (threadIdx.x + i blockDim.x) * 4 .. + 3 in v[4 i ..].  The mean first, then the squared deviations: no cancellation between two large sums.
+// red: 64 floats of shared memory of this call's own.
 template <int N4>
 __device__ __forceinline__ void sw_stats(const float (&v)[4 * N4], int width, int center, float eps, float* red, float& mean, float& rstd) {
     mean = 0.0f;
@@ -27,7 +39,7 @@ __device__ __forceinline__ void sw_stats(const float (&v)[4 * N4], int width, in
 #pragma unroll
         for (int i = 0; i < N4; i++)
             if ((int)(threadIdx.x + i * blockDim.x) * 4 < width) s += (v[4 * i] + v[4 * i + 1]) + (v[4 * i + 2] + v[4 * i + 3]);
-        mean = block_sum(s, red) / (float)width;
+        mean = sw_block_sum(s, red) / (float)width;
     }
     float ss = 0.0f;
 #pragma unroll
@@ -36,7 +48,7 @@ __device__ __forceinline__ void sw_stats(const float (&v)[4 * N4], int width, in
             const float d0 = v[4 * i] - mean, d1 = v[4 * i + 1] - mean, d2 = v[4 * i + 2] - mean, d3 = v[4 * i + 3] - mean;
             ss += (d0 * d0 + d1 * d1) + (d2 * d2 + d3 * d3);
         }
-    rstd = 1.0f / sqrtf(block_sum(ss, red) / (float)width + eps);
+    rstd = 1.0f / sqrtf(sw_block_sum(ss, red + 32) / (float)width + eps);
 }
 
 // out = norm(x[rows[o]]) as a product operand.  rows: optional gather.
@@ -177,12 +189,13 @@ __global__ void __launch_bounds__(256) k_embed_norm(PassTables t, const bf16* __
 // stay in registers between the passes (16-byte accesses); wider or unaligned rows walk the row again.  With a router (rn.w; few rows) the
 // kernel also forms the next sublayer's router logits from the operand row it has just written and picks the experts; dynamic shared
 // memory: width + 3 n_exp + n_groups floats.
-constexpr int SW_KEEP = 4;
-template <typename OT>
-__global__ void __launch_bounds__(256) k_sandwich_add(const float* __restrict__ Y, const float* __restrict__ Y2, const float* __restrict__ Yg,
+// SW_KEEP: float4 groups a thread keeps per array (1, 2 or 4: rows up to 1024, 2048, 4096 wide); fewer kept values, fewer registers, more rows
+// in flight per SM -- the kernel is bound by the latency of a row's load / reduce / store chain, not by bandwidth.
+template <typename OT, int SW_KEEP>
+__global__ void __launch_bounds__(256, SW_KEEP == 4 ? 4 : SW_KEEP == 2 ? 6 : 8) k_sandwich_add(const float* __restrict__ Y, const float* __restrict__ Y2, const float* __restrict__ Yg,
                                                       const int* __restrict__ pair_dst, int top, int width, NormArgs post, float* __restrict__ x,
                                                       NormArgs next, OT* __restrict__ op, int ld_op, GroupRouteNext rn) {
-    __shared__ float red[33];
+    __shared__ float red[128];           // four reductions, each with 32 floats of its own (the walking path uses the first 33)
     __shared__ int sdst[PN_MAX_TOP];
     extern __shared__ float srt[];
     const int r = blockIdx.x;
@@ -221,7 +234,7 @@ __global__ void __launch_bounds__(256) k_sandwich_add(const float* __restrict__ 
             }
         }
         if (!next.w) return;
-        sw_stats<SW_KEEP>(vx, width, cn, next.eps, red, mean, rstd);
+        sw_stats<SW_KEEP>(vx, width, cn, next.eps, red + 64, mean, rstd);
 #pragma unroll
         for (int i = 0; i < SW_KEEP; i++) {
             const int c = (threadIdx.x + i * blockDim.x) * 4;
