@@ -63,6 +63,20 @@ def test_registry_and_checkpoint_folder(tmp_path):
     assert set(back) == set(VU.tensor_shapes(desc)) and all(np.array_equal(back[k], t[k]) for k in t)
 
 
+def test_enumerators_follow_the_header():
+    import re
+    from pathlib import Path
+    hdr = (Path(__file__).resolve().parent.parent / "include" / "gten_b200_seq.h").read_text()
+    enums = dict(re.findall(r"(GTB_[A-Z0-9_]+) = (\d+)", hdr))
+    for name, value in (("BLOCK_SANDWICH", seq.BLOCK_SANDWICH), ("NORM_LAYER", seq.NORM_LAYER), ("FF_SWIGLU", seq.FF_SWIGLU), ("FF_GROUP_EXPERTS", seq.FF_GROUP_EXPERTS),
+                        ("MIX_RETENTION", seq.MIX_RETENTION), ("ROT_HALVES", seq.ROT_HALVES), ("ROT_INTERLEAVED", seq.ROT_INTERLEAVED)):
+        assert int(enums["GTB_" + name]) == value, name
+    for field in ("chunk", "maps", "diff", "bias", "act", "rot_divide"):
+        assert field in [f[0] for f in seq.BranchC._fields_]
+    for field in ("route_groups", "route_keep", "route_scale"):
+        assert field in [f[0] for f in seq.LayerC._fields_]
+
+
 def test_restatement_norms_and_rotation():
     rng = np.random.default_rng(0)
     x = rng.standard_normal((5, 12)) * 3 + 2
